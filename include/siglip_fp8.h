@@ -1,0 +1,211 @@
+/*
+ * siglip_fp8.h -- C ABI of libsiglip_fp8.so
+ *
+ * FP8 (e4m3) GEMM engine for the three dense contractions of a SigLIP ViT
+ * encoder block on NVIDIA B200 (sm_100a):
+ *
+ *     patch-embed : D = bf16( bf16(sa*sb * A.B^T) + table[(m + row_phase) % period, n] )
+ *     FC1 + GELU  : D = cast( gelu_tanh(sa*sb * A.B^T + bias[n]) / out_scale )
+ *     FC2 + res.  : D = bf16( sa*sb * A.B^T + bias[n] + residual[m, n] )
+ *
+ * Operand conventions are those of the reference project's per-layer launch
+ * points (stephendliang/siglip):
+ *     A [M, K] e4m3, K contiguous   (patch_embed.cu:159-160  tensor map dims {K, M})
+ *     B [N, K] e4m3, K contiguous   (patch_embed.cu:172-173  dims {K, N}: weights stored out x in)
+ *     D [M, N] bf16, N contiguous   (patch_embed.cu:187-188  dims {N, M})
+ * and each sl8_* layer call replaces one of its kernel launches
+ *     persistent_gemm<Op><<<148, 192, SMEM_BYTES>>>(tma_a, tma_b, tma_c, side_data, C, residual)
+ * (kernel_body.cuh:448-457) together with the three cuTensorMapEncodeTiled calls
+ * and the cudaFuncSetAttribute call that precede it in each layer's main().
+ *
+ * Differences from the reference launch, all additive:
+ *   - M, N, K and the leading dimensions are run-time arguments (the reference
+ *     fixes them at compile time, kernel_common.cuh:78-92);
+ *   - per-tensor dequantisation scales scale_a / scale_b multiply the FP32
+ *     accumulator before the epilogue (the reference consumes raw codes, i.e.
+ *     scale 1); they are DEVICE pointers to one float, NULL meaning 1.0f;
+ *   - FC1 can emit e4m3 directly (for the FC1 -> FC2 chain);
+ *   - the positional table is a plain row-major [period, N] bf16 array (the
+ *     reference wants a 32x32-blocked bias+pos table, patch_embed.cu:79-98).
+ *
+ * All pointers except `h`, the handle, are device pointers unless the function
+ * name ends in _host.  Calls are asynchronous with respect to the host and
+ * ordered on `stream` like a kernel launch.  Nothing is allocated on the call
+ * path of the device-pointer entry points.
+ *
+ * Alignment rules (checked; violation returns SL8_ERR_ALIGNMENT):
+ *   A, B, D, residual, table base addresses: 16 bytes;
+ *   lda, ldb (elements = bytes): multiples of 16; ldd, ldr, ld of table in
+ *   elements: such that the row pitch in bytes is a multiple of 16;
+ *   N must be a multiple of 16.  K and M are arbitrary (>= 1).
+ */
+#ifndef SIGLIP_FP8_H_
+#define SIGLIP_FP8_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct sl8_context* sl8_handle_t;
+
+/* cudaStream_t without dragging the CUDA headers into C callers. */
+typedef void* sl8_stream_t;
+
+/* ---- status codes (0 = success, negative = failure); never exit(), never throw:
+ * the reference's CUDA_CHECK / CU_CHECK print and exit(1) (kernel_common.cuh:123-138). */
+enum {
+    SL8_OK                 = 0,
+    SL8_ERR_INVALID_VALUE  = -1,  /* NULL pointer, non-positive size, unknown enum            */
+    SL8_ERR_ALIGNMENT      = -2,  /* base pointer or pitch breaks the 16-byte rules above      */
+    SL8_ERR_UNSUPPORTED    = -3,  /* shape outside what the kernels cover (e.g. N % 16 != 0)   */
+    SL8_ERR_CUDA           = -4,  /* a CUDA runtime / driver call failed; see sl8_last_error   */
+    SL8_ERR_DEVICE_TIMEOUT = -5,  /* a bounded device-side wait expired (sl8_device_status)    */
+    SL8_ERR_ARCH           = -6,  /* device is not compute capability 10.0                     */
+    SL8_ERR_NO_DEVICE      = -7   /* no CUDA device / driver                                   */
+};
+
+/* Output element type of FC1. */
+enum { SL8_OUT_BF16 = 0, SL8_OUT_E4M3 = 1 };
+
+/* Layer ids, in the order of the reference's EpilogueOp (kernel_body.cuh:8). */
+enum { SL8_OP_PATCH_EMBED = 0, SL8_OP_FC1_GELU = 1, SL8_OP_FC2_RESIDUAL = 2 };
+
+/* Flags (bitwise or). */
+enum {
+    SL8_FLAG_NONE        = 0,
+    /* bias is fp32 [N] as in the reference (kernel_body.cuh:12-13) instead of bf16 [N]. */
+    SL8_FLAG_BIAS_F32    = 1,
+    /* patch-embed: add the table in fp32 and round once, instead of the reference's
+     * bf16-domain add of bf16(acc) and the table (patch_embed.cu:44-58). */
+    SL8_FLAG_PE_F32_ADD  = 2
+};
+
+/* Which kernel variant the dispatch table picks for a problem. */
+typedef struct sl8_config {
+    int cta_group;     /* 1 = one CTA per tile, 2 = CTA pair (tcgen05 cta_group::2)        */
+    int tile_m;        /* rows per tile (128 * cta_group)                                    */
+    int tile_n;        /* columns per tile                                                   */
+    int tile_k;        /* K bytes per pipeline stage                                         */
+    int stages;        /* depth of the TMA -> MMA shared-memory ring                          */
+    int epi_warps;     /* epilogue warps per CTA                                              */
+    int tma_store;     /* 1 = swizzled shared staging + TMA tensor store, 0 = direct stores  */
+    int grid;          /* CTAs launched                                                      */
+    int smem_bytes;    /* dynamic shared memory per CTA                                      */
+    int variant_id;    /* index usable with SL8_FORCE_VARIANT / sl8_set_variant              */
+} sl8_config;
+
+/* ---- life cycle ------------------------------------------------------------------- */
+
+/* Creates a handle bound to CUDA device `device`.  Owns: one 16-byte device status
+ * block, the dispatch table, and (only if a *_host entry point is used) pinned and
+ * device staging buffers.  Replaces the per-main() setup at patch_embed.cu:104-200. */
+int sl8_create(sl8_handle_t* h, int device);
+int sl8_destroy(sl8_handle_t h);
+
+/* Text of the last failure on this handle (never NULL).  With h == NULL: the last
+ * failure of sl8_create on the calling thread. */
+const char* sl8_last_error_string(sl8_handle_t h);
+
+/* Library identification: "siglip_fp8 <version> sm_100a". */
+const char* sl8_version(void);
+
+/* ---- the three layers ---------------------------------------------------------------- */
+
+/* Patch-embed GEMM + periodic table add.  Replaces persistent_gemm<BIAS_ADD>
+ * (patch_embed.cu:200,216; epilogue patch_embed.cu:44-58; row -> table row
+ * kernel_body.cuh:71).  `table` is bf16 [period, N] with leading dimension ld_table
+ * (elements); the reference's table is bf16(bias + pos) (patch_embed.cu:79-98) -- the
+ * caller folds the bias in the same way.  row_phase shifts the period for shards that
+ * do not start on an image boundary: row m uses table row (m + row_phase) % period. */
+int sl8_patch_embed_fp8(sl8_handle_t h,
+                        const void* A, int64_t lda,
+                        const void* B, int64_t ldb,
+                        const float* scale_a, const float* scale_b,
+                        const void* table, int64_t ld_table, int period, int row_phase,
+                        void* D, int64_t ldd,
+                        int64_t M, int N, int K,
+                        unsigned flags, sl8_stream_t stream);
+
+/* FC1 GEMM + bias + GELU(tanh).  Replaces persistent_gemm<BIAS_GELU>
+ * (fc1_gelu.cu:131,147; gelu_fwd fc1_gelu.cu:16-19).  out_dtype SL8_OUT_BF16 writes
+ * bf16(g); SL8_OUT_E4M3 writes e4m3_sat_rne(g * (1 / *out_scale)), out_scale a device
+ * pointer to one float (NULL = 1).  ldd is in elements of the output type. */
+int sl8_fc1_gelu_fp8(sl8_handle_t h,
+                     const void* A, int64_t lda,
+                     const void* B, int64_t ldb,
+                     const float* scale_a, const float* scale_b,
+                     const void* bias,
+                     void* D, int64_t ldd, int out_dtype, const float* out_scale,
+                     int64_t M, int N, int K,
+                     unsigned flags, sl8_stream_t stream);
+
+/* FC2 GEMM + bias + residual.  Replaces persistent_gemm<BIAS_RESIDUAL>
+ * (fc2.cu:162,178; epilogue fc2.cu:19-54): D = bf16((acc + bias) + float(residual)). */
+int sl8_fc2_residual_fp8(sl8_handle_t h,
+                         const void* A, int64_t lda,
+                         const void* B, int64_t ldb,
+                         const float* scale_a, const float* scale_b,
+                         const void* bias,
+                         const void* residual, int64_t ldr,
+                         void* D, int64_t ldd,
+                         int64_t M, int N, int K,
+                         unsigned flags, sl8_stream_t stream);
+
+/* ---- the same three layers with HOST operands ------------------------------------------
+ * What each reference main() does around its launch (upload operands, launch, download
+ * all of C: patch_embed.cu:111-154,249-252), as one call: rows are cut into slabs that
+ * are uploaded, computed and downloaded on three streams so the copies overlap the
+ * kernels.  A, residual and D are host pointers (pinned memory gives full PCIe speed);
+ * B, bias, table and the scale/out_scale VALUES are host data too and are uploaded once
+ * per call.  Blocking: returns when D is complete in host memory.  Staging buffers are
+ * allocated by the handle on first use and kept. */
+int sl8_patch_embed_fp8_host(sl8_handle_t h,
+                             const void* A, int64_t lda, const void* B, int64_t ldb,
+                             float scale_a, float scale_b,
+                             const void* table, int64_t ld_table, int period, int row_phase,
+                             void* D, int64_t ldd, int64_t M, int N, int K, unsigned flags);
+int sl8_fc1_gelu_fp8_host(sl8_handle_t h,
+                          const void* A, int64_t lda, const void* B, int64_t ldb,
+                          float scale_a, float scale_b, const void* bias,
+                          void* D, int64_t ldd, int out_dtype, float out_scale,
+                          int64_t M, int N, int K, unsigned flags);
+int sl8_fc2_residual_fp8_host(sl8_handle_t h,
+                              const void* A, int64_t lda, const void* B, int64_t ldb,
+                              float scale_a, float scale_b, const void* bias,
+                              const void* residual, int64_t ldr,
+                              void* D, int64_t ldd, int64_t M, int N, int K, unsigned flags);
+
+/* ---- dispatch ------------------------------------------------------------------------- */
+
+/* Variant the dispatch table selects for (op, out_dtype, M, N, K); the reference has a
+ * single compile-time configuration (kernel_common.cuh:18-51,86-88). */
+int sl8_query_config(sl8_handle_t h, int op, int out_dtype, int64_t M, int N, int K, sl8_config* out);
+
+/* Number of compiled variants, and the description of variant `variant_id`. */
+int sl8_num_variants(void);
+int sl8_describe_variant(int variant_id, sl8_config* out);
+
+/* Forces every later call on this handle to use `variant_id` (-1 restores the table).
+ * The environment variable SL8_FORCE_VARIANT does the same for new handles. */
+int sl8_set_variant(sl8_handle_t h, int variant_id);
+
+/* ---- device-side wait watchdog -------------------------------------------------------- */
+
+/* Every wait inside the kernels (mbarrier polls) is bounded; a wait that expires records
+ * a code in the handle's device status block and the kernel unwinds and exits normally
+ * (the reference's mbar_wait spins for ever, kernel_common.cuh:166-178).
+ * sl8_device_status synchronises `stream`, reads the block, clears it, and returns SL8_OK
+ * or SL8_ERR_DEVICE_TIMEOUT; *detail (optional) receives role, barrier and tile of
+ * the first wait that expired. */
+int sl8_device_status(sl8_handle_t h, sl8_stream_t stream, unsigned detail[4]);
+
+/* Wait budget in milliseconds for later launches on this handle (default 2000). */
+int sl8_set_wait_budget_ms(sl8_handle_t h, int ms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SIGLIP_FP8_H_ */

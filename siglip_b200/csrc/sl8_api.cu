@@ -1,0 +1,638 @@
+// sl8_api.cu -- the C ABI of libsiglip_fp8.so (include/siglip_fp8.h): handle life cycle,
+// argument validation, tensor-map encoding, the dispatch table and the launches.
+//
+// This file plays the part of the host half of each reference layer's main()
+// (patch_embed.cu:104-246, fc1_gelu.cu:52-170, fc2.cu:72-200): it builds the three tensor
+// maps, raises the dynamic shared-memory limit and launches the persistent kernel -- for
+// run-time shapes, and returning status codes instead of exiting.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include "../../include/siglip_fp8.h"
+#include "sl8_variants.h"
+
+#define SL8_API extern "C" __attribute__((visibility("default")))
+
+namespace {
+
+using sl8::KernelParams;
+using sl8::VariantEntry;
+
+typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+const VariantEntry* variant(int id) {
+    switch (id) {
+#define SL8_CASE(id_, CG, TN, ST, EW, TS) \
+    case id_:                             \
+        return sl8_variant_##id_();
+        SL8_VARIANT_LIST(SL8_CASE)
+#undef SL8_CASE
+        default:
+            return nullptr;
+    }
+}
+
+thread_local std::string g_create_error;
+
+// Staging owned by the handle for the *_host entry points.
+struct HostPipe {
+    static const int SLOTS = 3;
+    cudaStream_t stream[SLOTS] = {nullptr, nullptr, nullptr};
+    cudaEvent_t consts_ready = nullptr;
+    void* d_a[SLOTS] = {nullptr, nullptr, nullptr};
+    void* d_r[SLOTS] = {nullptr, nullptr, nullptr};
+    void* d_d[SLOTS] = {nullptr, nullptr, nullptr};
+    size_t a_bytes = 0, r_bytes = 0, d_bytes = 0;
+    void* d_b = nullptr;      size_t b_bytes = 0;
+    void* d_bias = nullptr;   size_t bias_bytes = 0;
+    void* d_table = nullptr;  size_t table_bytes = 0;
+    float* d_scales = nullptr;   // scale_a, scale_b, out_scale
+    float* h_scales = nullptr;   // pinned twin
+    bool ready = false;
+};
+
+}  // namespace
+
+struct sl8_context {
+    int device = 0;
+    int sm_count = 0;
+    uint32_t* d_status = nullptr;       // 4 words
+    encode_tiled_fn encode = nullptr;
+    int forced_variant = -1;
+    unsigned wait_budget_ms = 2000;
+    bool smem_attr_set[SL8_NUM_VARIANTS][sl8::K_COUNT] = {};
+    int max_clusters[SL8_NUM_VARIANTS][sl8::K_COUNT] = {};
+    std::mutex mu;
+    std::string err;
+    HostPipe pipe;
+};
+
+namespace {
+
+int fail(sl8_handle_t h, int code, const std::string& msg) {
+    if (h) h->err = msg;
+    else g_create_error = msg;
+    return code;
+}
+
+int fail_cuda(sl8_handle_t h, cudaError_t e, const char* what) {
+    return fail(h, SL8_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+        if (prev != dev) ok = cudaSetDevice(dev) == cudaSuccess;
+    }
+    ~DeviceGuard() {
+        int cur = -1;
+        if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
+    }
+};
+
+// ---- dispatch -------------------------------------------------------------------------
+// Chosen from the sweep recorded in profiles/ (one line per rule; the first match wins).
+int pick_variant(int op, int out_dtype, long long M, int N, int K) {
+    (void)out_dtype;
+    (void)K;
+    const long long tiles256 = ((M + 255) / 256) * ((N + 255) / 256);
+    if (tiles256 < 74) {
+        // Too few 256 x 256 tiles to fill the GPU: smaller tiles give more of the 148 SMs work.
+        return (M <= 128) ? 8 : 9;
+    }
+    if (op == SL8_OP_FC2_RESIDUAL || op == SL8_OP_PATCH_EMBED) {
+        // N = 1152 is 6 x 192 exactly; 256-wide tiles would waste 10 % of the MMAs.
+        if (N % 256 != 0 && N % 192 == 0) return 6;
+    }
+    return 3;
+}
+
+struct Problem {
+    int op;
+    int out_dtype;
+    const void *A, *B;
+    long long lda, ldb;
+    const float *scale_a, *scale_b, *out_scale;
+    const void* bias;
+    const void* side;
+    long long ld_side;
+    int period, row_phase;
+    void* D;
+    long long ldd;
+    long long M;
+    int N, K;
+    unsigned flags;
+};
+
+int validate(sl8_handle_t h, const Problem& q) {
+    if (!h) return SL8_ERR_INVALID_VALUE;
+    if (!q.A || !q.B || !q.D) return fail(h, SL8_ERR_INVALID_VALUE, "A, B and D must not be NULL");
+    if (q.M < 1 || q.N < 1 || q.K < 1) return fail(h, SL8_ERR_INVALID_VALUE, "M, N, K must be positive");
+    if (q.M > 0x7FFFFF00ll) return fail(h, SL8_ERR_UNSUPPORTED, "M exceeds 2^31 rows");
+    if (q.out_dtype != SL8_OUT_BF16 && q.out_dtype != SL8_OUT_E4M3)
+        return fail(h, SL8_ERR_INVALID_VALUE, "unknown out_dtype");
+    if (q.flags & ~(unsigned)(SL8_FLAG_BIAS_F32 | SL8_FLAG_PE_F32_ADD)) return fail(h, SL8_ERR_INVALID_VALUE, "unknown flag bits");
+    if (q.N % 16 != 0) return fail(h, SL8_ERR_UNSUPPORTED, "N must be a multiple of 16");
+    if (q.lda < q.K || q.ldb < q.K) return fail(h, SL8_ERR_INVALID_VALUE, "lda / ldb smaller than K");
+    if (q.ldd < q.N) return fail(h, SL8_ERR_INVALID_VALUE, "ldd smaller than N");
+    const int ob = (q.out_dtype == SL8_OUT_BF16) ? 2 : 1;
+    if (!aligned16(q.A) || !aligned16(q.B) || !aligned16(q.D)) return fail(h, SL8_ERR_ALIGNMENT, "A, B, D must be 16-byte aligned");
+    if (q.lda % 16 || q.ldb % 16) return fail(h, SL8_ERR_ALIGNMENT, "lda and ldb must be multiples of 16 bytes");
+    if ((q.ldd * ob) % 16) return fail(h, SL8_ERR_ALIGNMENT, "row pitch of D must be a multiple of 16 bytes");
+    if (q.op == SL8_OP_PATCH_EMBED) {
+        if (!q.side) return fail(h, SL8_ERR_INVALID_VALUE, "table must not be NULL");
+        if (q.period < 1 || q.row_phase < 0) return fail(h, SL8_ERR_INVALID_VALUE, "period must be positive, row_phase non-negative");
+        if (q.ld_side < q.N) return fail(h, SL8_ERR_INVALID_VALUE, "ld_table smaller than N");
+        if (!aligned16(q.side) || (q.ld_side * 2) % 16) return fail(h, SL8_ERR_ALIGNMENT, "table must be 16-byte aligned with a 16-byte pitch");
+    }
+    if (q.op == SL8_OP_FC2_RESIDUAL) {
+        if (!q.side) return fail(h, SL8_ERR_INVALID_VALUE, "residual must not be NULL");
+        if (q.ld_side < q.N) return fail(h, SL8_ERR_INVALID_VALUE, "ldr smaller than N");
+        if (!aligned16(q.side) || (q.ld_side * 2) % 16) return fail(h, SL8_ERR_ALIGNMENT, "residual must be 16-byte aligned with a 16-byte pitch");
+    }
+    if (q.bias && !aligned16(q.bias)) return fail(h, SL8_ERR_ALIGNMENT, "bias must be 16-byte aligned");
+    if (q.scale_a && (reinterpret_cast<uintptr_t>(q.scale_a) & 3u)) return fail(h, SL8_ERR_ALIGNMENT, "scale pointers must be 4-byte aligned");
+    if (q.scale_b && (reinterpret_cast<uintptr_t>(q.scale_b) & 3u)) return fail(h, SL8_ERR_ALIGNMENT, "scale pointers must be 4-byte aligned");
+    if (q.out_scale && (reinterpret_cast<uintptr_t>(q.out_scale) & 3u)) return fail(h, SL8_ERR_ALIGNMENT, "scale pointers must be 4-byte aligned");
+    return SL8_OK;
+}
+
+int kernel_slot(int op, int out_dtype) {
+    if (op == SL8_OP_PATCH_EMBED) return sl8::K_PE;
+    if (op == SL8_OP_FC2_RESIDUAL) return sl8::K_FC2;
+    return out_dtype == SL8_OUT_E4M3 ? sl8::K_FC1_E4M3 : sl8::K_FC1_BF16;
+}
+
+int encode_2d(sl8_handle_t h, CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* base,
+              unsigned long long inner, unsigned long long outer, unsigned long long pitch_bytes, unsigned box_inner,
+              unsigned box_outer, CUtensorMapL2promotion promo) {
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    (void)elem_bytes;
+    CUresult r = h->encode(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        char buf[160];
+        snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled failed (CUresult %d) dims {%llu,%llu} pitch %llu box {%u,%u}",
+                 (int)r, inner, outer, pitch_bytes, box_inner, box_outer);
+        return fail(h, SL8_ERR_CUDA, buf);
+    }
+    return SL8_OK;
+}
+
+int grid_for(sl8_handle_t h, const VariantEntry* v, int slot, int num_tiles) {
+    int& cached = h->max_clusters[v->id][slot];
+    if (cached == 0) {
+        int clusters = h->sm_count / v->cg;
+        if (v->cg == 2) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(static_cast<unsigned>(h->sm_count / 2 * 2), 1, 1);
+            cfg.blockDim = dim3(static_cast<unsigned>(v->threads), 1, 1);
+            cfg.dynamicSmemBytes = static_cast<size_t>(v->smem_bytes[slot]);
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 2;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, v->kernel[slot], &cfg) == cudaSuccess && n > 0 && n < clusters) clusters = n;
+            else (void)cudaGetLastError();
+        }
+        cached = clusters > 0 ? clusters : 1;
+    }
+    const int clusters = num_tiles < cached ? num_tiles : cached;
+    return clusters * v->cg;
+}
+
+int run(sl8_handle_t h, const Problem& q, cudaStream_t stream) {
+    int rc = validate(h, q);
+    if (rc != SL8_OK) return rc;
+    std::lock_guard<std::mutex> lock(h->mu);
+    DeviceGuard guard(h->device);
+    if (!guard.ok) return fail(h, SL8_ERR_CUDA, "cudaSetDevice failed");
+
+    int vid = h->forced_variant >= 0 ? h->forced_variant : pick_variant(q.op, q.out_dtype, q.M, q.N, q.K);
+    const VariantEntry* v = variant(vid);
+    if (!v) return fail(h, SL8_ERR_INVALID_VALUE, "no such kernel variant");
+    const int slot = kernel_slot(q.op, q.out_dtype);
+    const int ob = (q.out_dtype == SL8_OUT_BF16) ? 2 : 1;
+
+    if (!h->smem_attr_set[vid][slot]) {
+        cudaError_t e = cudaFuncSetAttribute(v->kernel[slot], cudaFuncAttributeMaxDynamicSharedMemorySize, v->smem_bytes[slot]);
+        if (e != cudaSuccess) return fail_cuda(h, e, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize)");
+        h->smem_attr_set[vid][slot] = true;
+    }
+
+    CUtensorMap map_a, map_b, map_d;
+    rc = encode_2d(h, &map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q.A, (unsigned long long)q.K, (unsigned long long)q.M,
+                   (unsigned long long)q.lda, 128, 128, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+    if (rc != SL8_OK) return rc;
+    rc = encode_2d(h, &map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q.B, (unsigned long long)q.K, (unsigned long long)q.N,
+                   (unsigned long long)q.ldb, 128, (unsigned)(v->tn / v->cg), CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    if (rc != SL8_OK) return rc;
+    if (v->tma_store_slot[slot]) {
+        rc = encode_2d(h, &map_d, ob == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, ob, q.D,
+                       (unsigned long long)q.N, (unsigned long long)q.M, (unsigned long long)q.ldd * ob,
+                       (unsigned)(128 / ob), 32, CU_TENSOR_MAP_L2_PROMOTION_NONE);
+        if (rc != SL8_OK) return rc;
+    } else {
+        map_d = map_a;   // unused by the kernel; any valid map
+    }
+
+    KernelParams p;
+    memset(&p, 0, sizeof p);
+    p.M = q.M;
+    p.N = q.N;
+    p.K = q.K;
+    const int tile_m = 128 * v->cg;
+    const long long tiles_m = (q.M + tile_m - 1) / tile_m;
+    p.tiles_n = (q.N + v->tn - 1) / v->tn;
+    const long long nt = tiles_m * p.tiles_n;
+    if (nt > 0x7FFFFFFFll) return fail(h, SL8_ERR_UNSUPPORTED, "too many tiles");
+    p.num_tiles = static_cast<int>(nt);
+    p.k_blocks = (q.K + 127) / 128;
+    const int k_last = q.K - (p.k_blocks - 1) * 128;
+    p.last_kblock_mmas = (k_last + 31) / 32;
+    p.scale_a = q.scale_a;
+    p.scale_b = q.scale_b;
+    p.out_scale = q.out_scale;
+    p.bias = q.bias;
+    p.side = static_cast<const __nv_bfloat16*>(q.side);
+    p.ld_side = q.ld_side;
+    p.period = q.period > 0 ? q.period : 1;
+    p.row_phase = q.row_phase;
+    p.D = q.D;
+    p.ldd = q.ldd;
+    p.flags = q.flags;
+    p.wait_budget_ms = h->wait_budget_ms;
+    p.status = h->d_status;
+
+    const int grid = grid_for(h, v, slot, p.num_tiles);
+    cudaError_t e = v->launch[slot](&map_a, &map_b, &map_d, &p, grid, stream);
+    if (e != cudaSuccess) return fail_cuda(h, e, "kernel launch");
+    return SL8_OK;
+}
+
+void fill_config(const VariantEntry* v, int slot, int grid, sl8_config* out) {
+    out->cta_group = v->cg;
+    out->tile_m = 128 * v->cg;
+    out->tile_n = v->tn;
+    out->tile_k = 128;
+    out->stages = v->stages;
+    out->epi_warps = v->epi_warps;
+    out->tma_store = v->tma_store_slot[slot];
+    out->grid = grid;
+    out->smem_bytes = v->smem_bytes[slot];
+    out->variant_id = v->id;
+}
+
+}  // namespace
+
+// =========================================================================== life cycle
+
+SL8_API const char* sl8_version(void) { return "siglip_fp8 0.1 sm_100a"; }
+
+SL8_API int sl8_create(sl8_handle_t* out, int device) {
+    if (!out) return fail(nullptr, SL8_ERR_INVALID_VALUE, "handle pointer is NULL");
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        (void)cudaGetLastError();
+        return fail(nullptr, SL8_ERR_NO_DEVICE, std::string("no CUDA device: ") + cudaGetErrorString(e));
+    }
+    if (device < 0 || device >= count) return fail(nullptr, SL8_ERR_INVALID_VALUE, "device index out of range");
+    cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) return fail_cuda(nullptr, e, "cudaGetDeviceProperties");
+    if (prop.major != 10 || prop.minor != 0) {
+        char buf[128];
+        snprintf(buf, sizeof buf, "device %d is sm_%d%d; this library holds sm_100a code only", device, prop.major, prop.minor);
+        return fail(nullptr, SL8_ERR_ARCH, buf);
+    }
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(nullptr, SL8_ERR_CUDA, "cudaSetDevice failed");
+
+    sl8_context* h = new (std::nothrow) sl8_context();
+    if (!h) return fail(nullptr, SL8_ERR_CUDA, "out of host memory");
+    h->device = device;
+    h->sm_count = prop.multiProcessorCount;
+
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) {
+        delete h;
+        return fail(nullptr, SL8_ERR_CUDA, "cuTensorMapEncodeTiled not available from the driver");
+    }
+    h->encode = reinterpret_cast<encode_tiled_fn>(fn);
+
+    e = cudaMalloc(reinterpret_cast<void**>(&h->d_status), 16);
+    if (e != cudaSuccess) {
+        delete h;
+        return fail_cuda(nullptr, e, "cudaMalloc(status block)");
+    }
+    e = cudaMemset(h->d_status, 0, 16);
+    if (e != cudaSuccess) {
+        cudaFree(h->d_status);
+        delete h;
+        return fail_cuda(nullptr, e, "cudaMemset(status block)");
+    }
+    const char* fv = getenv("SL8_FORCE_VARIANT");
+    if (fv && *fv) {
+        const int id = atoi(fv);
+        if (id >= 0 && id < SL8_NUM_VARIANTS) h->forced_variant = id;
+    }
+    *out = h;
+    return SL8_OK;
+}
+
+SL8_API int sl8_destroy(sl8_handle_t h) {
+    if (!h) return SL8_ERR_INVALID_VALUE;
+    {
+        DeviceGuard guard(h->device);
+        cudaDeviceSynchronize();
+        HostPipe& pp = h->pipe;
+        for (int i = 0; i < HostPipe::SLOTS; i++) {
+            if (pp.d_a[i]) cudaFree(pp.d_a[i]);
+            if (pp.d_r[i]) cudaFree(pp.d_r[i]);
+            if (pp.d_d[i]) cudaFree(pp.d_d[i]);
+            if (pp.stream[i]) cudaStreamDestroy(pp.stream[i]);
+        }
+        if (pp.consts_ready) cudaEventDestroy(pp.consts_ready);
+        if (pp.d_b) cudaFree(pp.d_b);
+        if (pp.d_bias) cudaFree(pp.d_bias);
+        if (pp.d_table) cudaFree(pp.d_table);
+        if (pp.d_scales) cudaFree(pp.d_scales);
+        if (pp.h_scales) cudaFreeHost(pp.h_scales);
+        if (h->d_status) cudaFree(h->d_status);
+        (void)cudaGetLastError();
+    }
+    delete h;
+    return SL8_OK;
+}
+
+SL8_API const char* sl8_last_error_string(sl8_handle_t h) {
+    if (!h) return g_create_error.c_str();
+    return h->err.c_str();
+}
+
+// =========================================================================== layers
+
+SL8_API int sl8_patch_embed_fp8(sl8_handle_t h, const void* A, int64_t lda, const void* B, int64_t ldb,
+                                const float* scale_a, const float* scale_b, const void* table, int64_t ld_table,
+                                int period, int row_phase, void* D, int64_t ldd, int64_t M, int N, int K,
+                                unsigned flags, sl8_stream_t stream) {
+    Problem q = {};
+    q.op = SL8_OP_PATCH_EMBED; q.out_dtype = SL8_OUT_BF16;
+    q.A = A; q.B = B; q.lda = lda; q.ldb = ldb;
+    q.scale_a = scale_a; q.scale_b = scale_b;
+    q.side = table; q.ld_side = ld_table; q.period = period; q.row_phase = row_phase;
+    q.D = D; q.ldd = ldd; q.M = M; q.N = N; q.K = K; q.flags = flags;
+    return run(h, q, static_cast<cudaStream_t>(stream));
+}
+
+SL8_API int sl8_fc1_gelu_fp8(sl8_handle_t h, const void* A, int64_t lda, const void* B, int64_t ldb,
+                             const float* scale_a, const float* scale_b, const void* bias, void* D, int64_t ldd,
+                             int out_dtype, const float* out_scale, int64_t M, int N, int K, unsigned flags,
+                             sl8_stream_t stream) {
+    Problem q = {};
+    q.op = SL8_OP_FC1_GELU; q.out_dtype = out_dtype;
+    q.A = A; q.B = B; q.lda = lda; q.ldb = ldb;
+    q.scale_a = scale_a; q.scale_b = scale_b; q.out_scale = out_scale;
+    q.bias = bias;
+    q.D = D; q.ldd = ldd; q.M = M; q.N = N; q.K = K; q.flags = flags;
+    return run(h, q, static_cast<cudaStream_t>(stream));
+}
+
+SL8_API int sl8_fc2_residual_fp8(sl8_handle_t h, const void* A, int64_t lda, const void* B, int64_t ldb,
+                                 const float* scale_a, const float* scale_b, const void* bias, const void* residual,
+                                 int64_t ldr, void* D, int64_t ldd, int64_t M, int N, int K, unsigned flags,
+                                 sl8_stream_t stream) {
+    Problem q = {};
+    q.op = SL8_OP_FC2_RESIDUAL; q.out_dtype = SL8_OUT_BF16;
+    q.A = A; q.B = B; q.lda = lda; q.ldb = ldb;
+    q.scale_a = scale_a; q.scale_b = scale_b;
+    q.bias = bias; q.side = residual; q.ld_side = ldr;
+    q.D = D; q.ldd = ldd; q.M = M; q.N = N; q.K = K; q.flags = flags;
+    return run(h, q, static_cast<cudaStream_t>(stream));
+}
+
+// =========================================================================== host operands
+
+namespace {
+
+int ensure(sl8_handle_t h, void** p, size_t* have, size_t need) {
+    if (*have >= need && *p) return SL8_OK;
+    if (*p) { cudaFree(*p); *p = nullptr; *have = 0; }
+    cudaError_t e = cudaMalloc(p, need);
+    if (e != cudaSuccess) return fail_cuda(h, e, "cudaMalloc(host-operand staging)");
+    *have = need;
+    return SL8_OK;
+}
+
+// Rows per slab: about 64 MiB of output, a multiple of 256 rows so slabs start on tile rows.
+long long slab_rows_for(long long M, int N, int K, int out_bytes, bool has_res) {
+    const double per_row = (double)K + (double)N * out_bytes + (has_res ? 2.0 * N : 0.0);
+    long long rows = (long long)(64.0 * 1024 * 1024 / per_row);
+    rows = (rows / 256) * 256;
+    if (rows < 256) rows = 256;
+    if (rows > M) rows = M;
+    return rows;
+}
+
+int run_host(sl8_handle_t h, Problem q, float scale_a, float scale_b, float out_scale) {
+    if (!h) return SL8_ERR_INVALID_VALUE;
+    if (!q.A || !q.B || !q.D) return fail(h, SL8_ERR_INVALID_VALUE, "A, B and D must not be NULL");
+    if (q.M < 1 || q.N < 1 || q.K < 1) return fail(h, SL8_ERR_INVALID_VALUE, "M, N, K must be positive");
+    if (q.lda < q.K || q.ldb < q.K || q.ldd < q.N) return fail(h, SL8_ERR_INVALID_VALUE, "leading dimension too small");
+    if (q.lda % 16 || q.ldb % 16) return fail(h, SL8_ERR_ALIGNMENT, "lda and ldb must be multiples of 16 bytes");
+    const int ob = (q.out_dtype == SL8_OUT_BF16) ? 2 : 1;
+    if ((q.ldd * ob) % 16) return fail(h, SL8_ERR_ALIGNMENT, "row pitch of D must be a multiple of 16 bytes");
+    const bool has_res = q.op == SL8_OP_FC2_RESIDUAL;
+    if (has_res && (!q.side || q.ld_side < q.N || (q.ld_side * 2) % 16)) return fail(h, SL8_ERR_INVALID_VALUE, "bad residual");
+    if (q.op == SL8_OP_PATCH_EMBED && (!q.side || q.period < 1 || q.ld_side < q.N || (q.ld_side * 2) % 16 || q.row_phase < 0))
+        return fail(h, SL8_ERR_INVALID_VALUE, "bad table");
+
+    DeviceGuard guard(h->device);
+    if (!guard.ok) return fail(h, SL8_ERR_CUDA, "cudaSetDevice failed");
+    HostPipe& pp = h->pipe;
+    cudaError_t e;
+    if (!pp.ready) {
+        for (int i = 0; i < HostPipe::SLOTS; i++) {
+            e = cudaStreamCreateWithFlags(&pp.stream[i], cudaStreamNonBlocking);
+            if (e != cudaSuccess) return fail_cuda(h, e, "cudaStreamCreate");
+        }
+        e = cudaEventCreateWithFlags(&pp.consts_ready, cudaEventDisableTiming);
+        if (e != cudaSuccess) return fail_cuda(h, e, "cudaEventCreate");
+        e = cudaMalloc(reinterpret_cast<void**>(&pp.d_scales), 16);
+        if (e != cudaSuccess) return fail_cuda(h, e, "cudaMalloc(scales)");
+        e = cudaMallocHost(reinterpret_cast<void**>(&pp.h_scales), 16);
+        if (e != cudaSuccess) return fail_cuda(h, e, "cudaMallocHost(scales)");
+        pp.ready = true;
+    }
+    const long long slab = slab_rows_for(q.M, q.N, q.K, ob, has_res);
+    int rc;
+    for (int i = 0; i < HostPipe::SLOTS; i++) {
+        size_t ha = pp.a_bytes, hd = pp.d_bytes, hr = pp.r_bytes;
+        if ((rc = ensure(h, &pp.d_a[i], &ha, (size_t)slab * q.lda)) != SL8_OK) return rc;
+        if ((rc = ensure(h, &pp.d_d[i], &hd, (size_t)slab * q.ldd * ob)) != SL8_OK) return rc;
+        if (has_res && (rc = ensure(h, &pp.d_r[i], &hr, (size_t)slab * q.ld_side * 2)) != SL8_OK) return rc;
+        if (i == HostPipe::SLOTS - 1) { pp.a_bytes = ha; pp.d_bytes = hd; pp.r_bytes = hr; }
+    }
+    if ((rc = ensure(h, &pp.d_b, &pp.b_bytes, (size_t)q.N * q.ldb)) != SL8_OK) return rc;
+    const size_t bias_need = (size_t)q.N * ((q.flags & SL8_FLAG_BIAS_F32) ? 4 : 2);
+    if (q.bias && (rc = ensure(h, &pp.d_bias, &pp.bias_bytes, bias_need)) != SL8_OK) return rc;
+    if (q.op == SL8_OP_PATCH_EMBED && (rc = ensure(h, &pp.d_table, &pp.table_bytes, (size_t)q.period * q.ld_side * 2)) != SL8_OK) return rc;
+
+    // constants, once per call, on slot 0's stream
+    cudaStream_t s0 = pp.stream[0];
+    pp.h_scales[0] = scale_a; pp.h_scales[1] = scale_b; pp.h_scales[2] = out_scale;
+    cudaMemcpyAsync(pp.d_scales, pp.h_scales, 12, cudaMemcpyHostToDevice, s0);
+    cudaMemcpyAsync(pp.d_b, q.B, (size_t)q.N * q.ldb, cudaMemcpyHostToDevice, s0);
+    if (q.bias) cudaMemcpyAsync(pp.d_bias, q.bias, bias_need, cudaMemcpyHostToDevice, s0);
+    if (q.op == SL8_OP_PATCH_EMBED) cudaMemcpyAsync(pp.d_table, q.side, (size_t)q.period * q.ld_side * 2, cudaMemcpyHostToDevice, s0);
+    e = cudaEventRecord(pp.consts_ready, s0);
+    if (e != cudaSuccess) return fail_cuda(h, e, "upload of constants");
+
+    const uint8_t* hA = static_cast<const uint8_t*>(q.A);
+    const uint8_t* hR = static_cast<const uint8_t*>(q.side);
+    uint8_t* hD = static_cast<uint8_t*>(q.D);
+    int slot = 0;
+    for (long long r0 = 0; r0 < q.M; r0 += slab, slot = (slot + 1) % HostPipe::SLOTS) {
+        const long long rows = (r0 + slab < q.M) ? slab : q.M - r0;
+        cudaStream_t s = pp.stream[slot];
+        if (slot != 0 || r0 == 0) cudaStreamWaitEvent(s, pp.consts_ready, 0);
+        cudaMemcpyAsync(pp.d_a[slot], hA + (size_t)r0 * q.lda, (size_t)rows * q.lda, cudaMemcpyHostToDevice, s);
+        if (has_res) cudaMemcpyAsync(pp.d_r[slot], hR + (size_t)r0 * q.ld_side * 2, (size_t)rows * q.ld_side * 2, cudaMemcpyHostToDevice, s);
+        Problem d = q;
+        d.A = pp.d_a[slot];
+        d.B = pp.d_b;
+        d.D = pp.d_d[slot];
+        d.M = rows;
+        d.bias = q.bias ? pp.d_bias : nullptr;
+        d.scale_a = pp.d_scales; d.scale_b = pp.d_scales + 1; d.out_scale = pp.d_scales + 2;
+        if (q.op == SL8_OP_PATCH_EMBED) { d.side = pp.d_table; d.row_phase = (int)((q.row_phase + r0) % q.period); }
+        if (has_res) d.side = pp.d_r[slot];
+        rc = run(h, d, s);
+        if (rc != SL8_OK) { cudaDeviceSynchronize(); return rc; }
+        cudaMemcpyAsync(hD + (size_t)r0 * q.ldd * ob, pp.d_d[slot], (size_t)rows * q.ldd * ob, cudaMemcpyDeviceToHost, s);
+    }
+    for (int i = 0; i < HostPipe::SLOTS; i++) {
+        e = cudaStreamSynchronize(pp.stream[i]);
+        if (e != cudaSuccess) return fail_cuda(h, e, "host-operand pipeline");
+    }
+    return SL8_OK;
+}
+
+}  // namespace
+
+SL8_API int sl8_patch_embed_fp8_host(sl8_handle_t h, const void* A, int64_t lda, const void* B, int64_t ldb,
+                                     float scale_a, float scale_b, const void* table, int64_t ld_table, int period,
+                                     int row_phase, void* D, int64_t ldd, int64_t M, int N, int K, unsigned flags) {
+    Problem q = {};
+    q.op = SL8_OP_PATCH_EMBED; q.out_dtype = SL8_OUT_BF16;
+    q.A = A; q.B = B; q.lda = lda; q.ldb = ldb;
+    q.side = table; q.ld_side = ld_table; q.period = period; q.row_phase = row_phase;
+    q.D = D; q.ldd = ldd; q.M = M; q.N = N; q.K = K; q.flags = flags;
+    return run_host(h, q, scale_a, scale_b, 1.0f);
+}
+
+SL8_API int sl8_fc1_gelu_fp8_host(sl8_handle_t h, const void* A, int64_t lda, const void* B, int64_t ldb, float scale_a,
+                                  float scale_b, const void* bias, void* D, int64_t ldd, int out_dtype, float out_scale,
+                                  int64_t M, int N, int K, unsigned flags) {
+    if (out_dtype != SL8_OUT_BF16 && out_dtype != SL8_OUT_E4M3) return fail(h, SL8_ERR_INVALID_VALUE, "unknown out_dtype");
+    Problem q = {};
+    q.op = SL8_OP_FC1_GELU; q.out_dtype = out_dtype;
+    q.A = A; q.B = B; q.lda = lda; q.ldb = ldb; q.bias = bias;
+    q.D = D; q.ldd = ldd; q.M = M; q.N = N; q.K = K; q.flags = flags;
+    return run_host(h, q, scale_a, scale_b, out_scale);
+}
+
+SL8_API int sl8_fc2_residual_fp8_host(sl8_handle_t h, const void* A, int64_t lda, const void* B, int64_t ldb,
+                                      float scale_a, float scale_b, const void* bias, const void* residual, int64_t ldr,
+                                      void* D, int64_t ldd, int64_t M, int N, int K, unsigned flags) {
+    Problem q = {};
+    q.op = SL8_OP_FC2_RESIDUAL; q.out_dtype = SL8_OUT_BF16;
+    q.A = A; q.B = B; q.lda = lda; q.ldb = ldb; q.bias = bias;
+    q.side = residual; q.ld_side = ldr;
+    q.D = D; q.ldd = ldd; q.M = M; q.N = N; q.K = K; q.flags = flags;
+    return run_host(h, q, scale_a, scale_b, 1.0f);
+}
+
+// =========================================================================== dispatch
+
+SL8_API int sl8_num_variants(void) { return SL8_NUM_VARIANTS; }
+
+SL8_API int sl8_describe_variant(int variant_id, sl8_config* out) {
+    const VariantEntry* v = variant(variant_id);
+    if (!v || !out) return SL8_ERR_INVALID_VALUE;
+    fill_config(v, sl8::K_FC1_BF16, 0, out);
+    return SL8_OK;
+}
+
+SL8_API int sl8_query_config(sl8_handle_t h, int op, int out_dtype, int64_t M, int N, int K, sl8_config* out) {
+    if (!out || M < 1 || N < 1 || K < 1 || op < 0 || op > 2) return SL8_ERR_INVALID_VALUE;
+    int vid = (h && h->forced_variant >= 0) ? h->forced_variant : pick_variant(op, out_dtype, M, N, K);
+    const VariantEntry* v = variant(vid);
+    if (!v) return SL8_ERR_INVALID_VALUE;
+    const int slot = kernel_slot(op, out_dtype);
+    const int tile_m = 128 * v->cg;
+    const long long nt = ((M + tile_m - 1) / tile_m) * ((N + v->tn - 1) / v->tn);
+    const int sms = h ? h->sm_count : 148;
+    long long clusters = sms / v->cg;
+    if (nt < clusters) clusters = nt;
+    fill_config(v, slot, (int)clusters * v->cg, out);
+    return SL8_OK;
+}
+
+SL8_API int sl8_set_variant(sl8_handle_t h, int variant_id) {
+    if (!h) return SL8_ERR_INVALID_VALUE;
+    if (variant_id >= SL8_NUM_VARIANTS) return fail(h, SL8_ERR_INVALID_VALUE, "no such kernel variant");
+    std::lock_guard<std::mutex> lock(h->mu);
+    h->forced_variant = variant_id < 0 ? -1 : variant_id;
+    return SL8_OK;
+}
+
+// =========================================================================== watchdog
+
+SL8_API int sl8_device_status(sl8_handle_t h, sl8_stream_t stream, unsigned detail[4]) {
+    if (!h) return SL8_ERR_INVALID_VALUE;
+    DeviceGuard guard(h->device);
+    cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail_cuda(h, e, "cudaStreamSynchronize");
+    uint32_t st[4] = {0, 0, 0, 0};
+    e = cudaMemcpy(st, h->d_status, 16, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail_cuda(h, e, "read of the status block");
+    if (detail) for (int i = 0; i < 4; i++) detail[i] = st[i];
+    if (st[0] == 0) return SL8_OK;
+    cudaMemset(h->d_status, 0, 16);
+    char buf[160];
+    static const char* names[] = {"", "producer waiting for a free stage", "MMA thread waiting for operands",
+                                  "MMA thread waiting for a free accumulator", "epilogue waiting for an accumulator"};
+    snprintf(buf, sizeof buf, "device wait expired: %s (index %u, tile %u, block %u)", st[0] < 5 ? names[st[0]] : "?", st[1],
+             st[2], st[3]);
+    return fail(h, SL8_ERR_DEVICE_TIMEOUT, buf);
+}
+
+SL8_API int sl8_set_wait_budget_ms(sl8_handle_t h, int ms) {
+    if (!h || ms < 1) return SL8_ERR_INVALID_VALUE;
+    h->wait_budget_ms = static_cast<unsigned>(ms);
+    return SL8_OK;
+}

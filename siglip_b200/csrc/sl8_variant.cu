@@ -1,0 +1,75 @@
+// sl8_variant.cu -- instantiates the four kernels (patch-embed, FC1 -> bf16, FC1 -> e4m3,
+// FC2) of ONE tile configuration and exports its table entry.  Compiled once per entry of
+// SL8_VARIANT_LIST with -DSL8_VARIANT_ID=<id>, so the configurations build in parallel.
+#include "sl8_variants.h"
+
+#ifndef SL8_VARIANT_ID
+#error "compile with -DSL8_VARIANT_ID=<id from SL8_VARIANT_LIST>"
+#endif
+
+namespace sl8 {
+namespace {
+
+template <int CG, int TN, int STAGES, int EW, int OP, int OUT, bool TS>
+cudaError_t launch_one(const CUtensorMap* map_a, const CUtensorMap* map_b, const CUtensorMap* map_d,
+                       const KernelParams* params, int grid, cudaStream_t stream) {
+    using T = KernelTraits<CG, TN, STAGES, EW, OUT, TS>;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+    cfg.blockDim = dim3(T::THREADS, 1, 1);
+    cfg.dynamicSmemBytes = T::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CG;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, sl8_gemm_kernel<CG, TN, STAGES, EW, OP, OUT, TS>, *map_a, *map_b, *map_d, *params);
+}
+
+template <int ID, int CG, int TN, int STAGES, int EW, bool TS>
+const VariantEntry* make_entry() {
+    // A staging row holds 128 e4m3 columns; where a warp's column range is not a whole number of
+    // such regions (TN = 192) the e4m3 kernel stores from registers instead.
+    constexpr bool TS8 = TS && ((TN / (EW / 4)) % 128 == 0);
+    static const VariantEntry e = {
+        ID, CG, TN, STAGES, EW, TS ? 1 : 0,
+        KernelTraits<CG, TN, STAGES, EW, OUT_BF16, TS>::THREADS,
+        {TS ? 1 : 0, TS ? 1 : 0, TS8 ? 1 : 0, TS ? 1 : 0},
+        {KernelTraits<CG, TN, STAGES, EW, OUT_BF16, TS>::SMEM_BYTES, KernelTraits<CG, TN, STAGES, EW, OUT_BF16, TS>::SMEM_BYTES,
+         KernelTraits<CG, TN, STAGES, EW, OUT_E4M3, TS8>::SMEM_BYTES, KernelTraits<CG, TN, STAGES, EW, OUT_BF16, TS>::SMEM_BYTES},
+        {reinterpret_cast<const void*>(&sl8_gemm_kernel<CG, TN, STAGES, EW, OP_PE, OUT_BF16, TS>),
+         reinterpret_cast<const void*>(&sl8_gemm_kernel<CG, TN, STAGES, EW, OP_FC1, OUT_BF16, TS>),
+         reinterpret_cast<const void*>(&sl8_gemm_kernel<CG, TN, STAGES, EW, OP_FC1, OUT_E4M3, TS8>),
+         reinterpret_cast<const void*>(&sl8_gemm_kernel<CG, TN, STAGES, EW, OP_FC2, OUT_BF16, TS>)},
+        {&launch_one<CG, TN, STAGES, EW, OP_PE, OUT_BF16, TS>, &launch_one<CG, TN, STAGES, EW, OP_FC1, OUT_BF16, TS>,
+         &launch_one<CG, TN, STAGES, EW, OP_FC1, OUT_E4M3, TS8>, &launch_one<CG, TN, STAGES, EW, OP_FC2, OUT_BF16, TS>}};
+    return &e;
+}
+
+}  // namespace
+}  // namespace sl8
+
+#define SL8_CAT2(a, b) a##b
+#define SL8_CAT(a, b) SL8_CAT2(a, b)
+
+#define SL8_DEFINE_IF_SELECTED(id, CG, TN, ST, EW, TS)                                     \
+    template <int SEL, typename = void>                                                    \
+    struct SL8_CAT(Pick, id) {                                                             \
+        static const sl8::VariantEntry* get() { return nullptr; }                          \
+    };                                                                                     \
+    template <typename V>                                                                  \
+    struct SL8_CAT(Pick, id)<id, V> {                                                      \
+        static const sl8::VariantEntry* get() { return sl8::make_entry<id, CG, TN, ST, EW, (TS) != 0>(); } \
+    };
+SL8_VARIANT_LIST(SL8_DEFINE_IF_SELECTED)
+#undef SL8_DEFINE_IF_SELECTED
+
+// Only the Pick<id> specialisation matching SL8_VARIANT_ID is ever instantiated, so only its
+// kernels are compiled into this object.
+#define SL8_ENTRY_NAME SL8_CAT(sl8_variant_, SL8_VARIANT_ID)
+#define SL8_PICK_NAME SL8_CAT(Pick, SL8_VARIANT_ID)
+
+extern "C" const sl8::VariantEntry* SL8_ENTRY_NAME() { return SL8_PICK_NAME<SL8_VARIANT_ID>::get(); }

@@ -1,0 +1,188 @@
+"""Host-side layer interface over torch tensors: the three launches of the reference's
+per-layer bench hosts (patch_embed.cu:216, fc1_gelu.cu:147, fc2.cu:178) as methods of one
+``Engine`` bound to a GPU.  torch supplies device memory and streams; all arithmetic happens
+inside libsiglip_fp8.so.
+
+Operand conventions (those of the reference): ``A`` is [M, K] e4m3 with K contiguous,
+``B`` is [N, K] e4m3 (weights stored out x in), outputs are [M, N] row-major.  e4m3
+tensors may be ``torch.float8_e4m3fn`` or raw ``torch.uint8`` codes.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import lib as _l
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _is_fp8(t: torch.Tensor) -> bool:
+    return t.dtype in (torch.uint8, torch.float8_e4m3fn)
+
+
+class Engine:
+    """One handle of libsiglip_fp8.so (``sl8_create``) on CUDA device ``device``."""
+
+    def __init__(self, device: int = 0):
+        self._lib = _l.load_library()
+        self._h = C.c_void_p()
+        self.device = int(device)
+        rc = self._lib.sl8_create(C.byref(self._h), self.device)
+        if rc != _l.SL8_OK:
+            raise _l.SL8Error(rc, self._lib.sl8_last_error_string(None).decode())
+
+    # ------------------------------------------------------------------ plumbing
+    def close(self) -> None:
+        if getattr(self, "_h", None) is not None and self._h.value:
+            self._lib.sl8_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def _check(self, rc: int) -> None:
+        if rc != _l.SL8_OK:
+            raise _l.SL8Error(rc, self._lib.sl8_last_error_string(self._h).decode())
+
+    def _stream(self, stream) -> int:
+        if stream is None:
+            stream = torch.cuda.current_stream(self.device)
+        return stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream)
+
+    def _operands(self, A: torch.Tensor, B: torch.Tensor):
+        if not (_is_fp8(A) and _is_fp8(B)):
+            raise TypeError("A and B must be float8_e4m3fn or uint8 (raw e4m3 codes)")
+        if A.dim() != 2 or B.dim() != 2 or A.stride(1) != 1 or B.stride(1) != 1:
+            raise ValueError("A [M, K] and B [N, K] must be 2-D with K contiguous")
+        if not (A.is_cuda and B.is_cuda):
+            raise ValueError("A and B must be CUDA tensors (use the *_host methods for host operands)")
+        M, K = A.shape
+        N, Kb = B.shape
+        if K != Kb:
+            raise ValueError(f"K mismatch: A has {K}, B has {Kb}")
+        return M, N, K
+
+    @staticmethod
+    def _new_out(M: int, N: int, dtype: torch.dtype, device) -> torch.Tensor:
+        return torch.empty((M, N), dtype=dtype, device=device)
+
+    # ------------------------------------------------------------------ layers
+    def patch_embed(self, A, B, table, *, scale_a=None, scale_b=None, row_phase: int = 0, out=None,
+                    flags: int = 0, stream=None) -> torch.Tensor:
+        """D = bf16(bf16(sa*sb*A.B^T) + table[(m + row_phase) % period]); table is bf16 [period, N]."""
+        M, N, K = self._operands(A, B)
+        if table.dtype != torch.bfloat16 or table.dim() != 2 or table.shape[1] != N or table.stride(1) != 1:
+            raise ValueError("table must be bf16 [period, N] with N contiguous")
+        D = self._new_out(M, N, torch.bfloat16, A.device) if out is None else out
+        self._check(self._lib.sl8_patch_embed_fp8(
+            self._h, A.data_ptr(), A.stride(0), B.data_ptr(), B.stride(0), _ptr(scale_a), _ptr(scale_b),
+            table.data_ptr(), table.stride(0), table.shape[0], int(row_phase), D.data_ptr(), D.stride(0),
+            M, N, K, int(flags), self._stream(stream)))
+        return D
+
+    def fc1_gelu(self, A, B, bias, *, scale_a=None, scale_b=None, out_dtype=torch.bfloat16, out_scale=None,
+                 out=None, flags: int = 0, stream=None) -> torch.Tensor:
+        """D = cast(gelu_tanh(sa*sb*A.B^T + bias) / out_scale); bias bf16 [N] (fp32 with SL8_FLAG_BIAS_F32)."""
+        M, N, K = self._operands(A, B)
+        if bias is not None and bias.dtype == torch.float32:
+            flags |= _l.SL8_FLAG_BIAS_F32
+        elif bias is not None and bias.dtype != torch.bfloat16:
+            raise TypeError("bias must be bf16 or fp32")
+        e4 = out_dtype in (torch.float8_e4m3fn, torch.uint8)
+        D = self._new_out(M, N, out_dtype, A.device) if out is None else out
+        self._check(self._lib.sl8_fc1_gelu_fp8(
+            self._h, A.data_ptr(), A.stride(0), B.data_ptr(), B.stride(0), _ptr(scale_a), _ptr(scale_b), _ptr(bias),
+            D.data_ptr(), D.stride(0), _l.SL8_OUT_E4M3 if e4 else _l.SL8_OUT_BF16, _ptr(out_scale), M, N, K,
+            int(flags), self._stream(stream)))
+        return D
+
+    def fc2_residual(self, A, B, bias, residual, *, scale_a=None, scale_b=None, out=None, flags: int = 0,
+                     stream=None) -> torch.Tensor:
+        """D = bf16((sa*sb*A.B^T + bias) + residual); residual bf16 [M, N]."""
+        M, N, K = self._operands(A, B)
+        if bias is not None and bias.dtype == torch.float32:
+            flags |= _l.SL8_FLAG_BIAS_F32
+        if residual.dtype != torch.bfloat16 or residual.shape != (M, N) or residual.stride(1) != 1:
+            raise ValueError("residual must be bf16 [M, N] with N contiguous")
+        D = self._new_out(M, N, torch.bfloat16, A.device) if out is None else out
+        self._check(self._lib.sl8_fc2_residual_fp8(
+            self._h, A.data_ptr(), A.stride(0), B.data_ptr(), B.stride(0), _ptr(scale_a), _ptr(scale_b), _ptr(bias),
+            residual.data_ptr(), residual.stride(0), D.data_ptr(), D.stride(0), M, N, K, int(flags),
+            self._stream(stream)))
+        return D
+
+    # ------------------------------------------------------------------ host operands
+    def patch_embed_host(self, A, B, table, out, *, scale_a=1.0, scale_b=1.0, row_phase=0, flags=0):
+        M, K = A.shape
+        N = B.shape[0]
+        self._check(self._lib.sl8_patch_embed_fp8_host(
+            self._h, A.data_ptr(), A.stride(0), B.data_ptr(), B.stride(0), float(scale_a), float(scale_b),
+            table.data_ptr(), table.stride(0), table.shape[0], int(row_phase), out.data_ptr(), out.stride(0),
+            M, N, K, int(flags)))
+        return out
+
+    def fc1_gelu_host(self, A, B, bias, out, *, scale_a=1.0, scale_b=1.0, out_scale=1.0, flags=0):
+        M, K = A.shape
+        N = B.shape[0]
+        if bias is not None and bias.dtype == torch.float32:
+            flags |= _l.SL8_FLAG_BIAS_F32
+        e4 = out.dtype in (torch.float8_e4m3fn, torch.uint8)
+        self._check(self._lib.sl8_fc1_gelu_fp8_host(
+            self._h, A.data_ptr(), A.stride(0), B.data_ptr(), B.stride(0), float(scale_a), float(scale_b),
+            _ptr(bias), out.data_ptr(), out.stride(0), _l.SL8_OUT_E4M3 if e4 else _l.SL8_OUT_BF16,
+            float(out_scale), M, N, K, int(flags)))
+        return out
+
+    def fc2_residual_host(self, A, B, bias, residual, out, *, scale_a=1.0, scale_b=1.0, flags=0):
+        M, K = A.shape
+        N = B.shape[0]
+        if bias is not None and bias.dtype == torch.float32:
+            flags |= _l.SL8_FLAG_BIAS_F32
+        self._check(self._lib.sl8_fc2_residual_fp8_host(
+            self._h, A.data_ptr(), A.stride(0), B.data_ptr(), B.stride(0), float(scale_a), float(scale_b),
+            _ptr(bias), residual.data_ptr(), residual.stride(0), out.data_ptr(), out.stride(0), M, N, K,
+            int(flags)))
+        return out
+
+    # ------------------------------------------------------------------ dispatch and watchdog
+    def query_config(self, op: int, M: int, N: int, K: int, out_dtype: int = _l.SL8_OUT_BF16) -> dict:
+        cfg = _l.Config()
+        self._check(self._lib.sl8_query_config(self._h, op, out_dtype, M, N, K, C.byref(cfg)))
+        return cfg.as_dict()
+
+    def set_variant(self, variant_id: int) -> None:
+        self._check(self._lib.sl8_set_variant(self._h, int(variant_id)))
+
+    def set_wait_budget_ms(self, ms: int) -> None:
+        self._check(self._lib.sl8_set_wait_budget_ms(self._h, int(ms)))
+
+    def device_status(self, stream=None) -> None:
+        """Synchronises the stream and raises SL8Error(SL8_ERR_DEVICE_TIMEOUT) if a device wait expired."""
+        detail = (C.c_uint * 4)()
+        self._check(self._lib.sl8_device_status(self._h, self._stream(stream), C.byref(detail)))
+
+
+def num_variants() -> int:
+    return _l.load_library().sl8_num_variants()
+
+
+def describe_variant(variant_id: int) -> dict:
+    cfg = _l.Config()
+    rc = _l.load_library().sl8_describe_variant(int(variant_id), C.byref(cfg))
+    if rc != _l.SL8_OK:
+        raise _l.SL8Error(rc, "no such variant")
+    return cfg.as_dict()
