@@ -1,0 +1,365 @@
+#!/usr/bin/env python
+"""Benchmark of the FP8 GEMM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config C2] [--layers]
+
+A step is one pass of the hot path over one batch of synthetic operands: one fused-GEMM
+launch of libsiglip_fp8.so.  The workload at every N is the configuration the headline
+metric is quoted on: SigLIP-So400m FC1 + bias + GELU(tanh), M = 46 656 rows (64 images x 729
+tokens), K = 1152, N = 4304, e4m3 operands with per-tensor scales, bf16 output.  With N GPUs
+every rank runs that workload on its own 64 images (rows are independent: no collective on
+the data path), so the scaling is weak and `value` is the sum over ranks.
+
+Rank 0 prints ONE JSON line.  `value` is TFLOP/s (2*M*N*K with the unpadded K and N) with the
+operands resident in HBM; `e2e` is the same metric through the host-operand entry point
+(pinned host buffers, host->device and device->host copies inside the timed region).
+`--impl reference` times the CPU restatement of the reference's algorithm on the host cores
+(the reference itself is CUDA-only, so there is no CPU build of it to run).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "fp8_tflops_fc1_gelu"
+UNIT = "TFLOP/s"
+
+
+# ----------------------------------------------------------------------------- peaks
+def measured_peaks() -> dict:
+    """Roofline denominators: the measured copy bandwidth and bf16 GEMM rate of this pool's B200s when
+    the driver wrote them; otherwise the stated fallback (6.65 TB/s, 1.59 PFLOP/s bf16).  The e4m3
+    tensor-core rate is twice the bf16 rate of the same tensor cores, so the FP8 peak is 2 x bf16."""
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        d = json.loads(f.read_text())
+        return dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]),
+                    bf16_tflops_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, device_index: int, period_s: float = 0.01):
+        self.samples, self.reasons = [], set()
+        self.sm_max = None
+        self._stop = threading.Event()
+        self._thread = None
+        self.period = period_s
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+            self.sm_max = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _one(self):
+        try:
+            self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+            mask = self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+            for bit, name in self.REASONS.items():
+                if mask & bit:
+                    self.reasons.add(name)
+        except Exception:
+            pass
+
+    def _run(self):
+        while not self._stop.is_set():
+            self._one()
+            self._stop.wait(self.period)
+
+    def start(self):
+        if self.nv is None:
+            return
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+
+    def stop(self) -> dict:
+        if self.nv is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml unavailable"]}
+        self._one()
+        self._stop.set()
+        self._thread.join()
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.sm_max, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def cpu_oracle_rate(cfg_name: str, target_seconds: float, seed: int = 0):
+    """Times the CPU restatement (oracle/) on a bounded row sample of the workload, all host threads.
+    Returns (TFLOP/s, cores, description, seconds)."""
+    from siglip_b200 import synth
+    from tests.oracle_lib import Oracle
+    orc = Oracle()
+    c = synth.CONFIGS[cfg_name]
+    rows_per_image = c["M"] // c["images"]
+
+    def run(images: int) -> float:
+        p = synth.make_config(cfg_name, seed=seed, images=images)
+        A, B = p.A.numpy(), p.B.numpy()
+        bias = p.bias.view(torch.uint16).numpy() if p.bias is not None else None
+        t0 = time.perf_counter()
+        if p.op == synth.OP_FC1_GELU:
+            orc.fc1_gelu(A, B, p.scale_a, p.scale_b, bias)
+        elif p.op == synth.OP_FC2_RESIDUAL:
+            orc.fc2_residual(A, B, p.scale_a, p.scale_b, bias, p.residual.view(torch.uint16).numpy())
+        else:
+            orc.patch_embed(A, B, p.scale_a, p.scale_b, p.table.view(torch.uint16).numpy())
+        return time.perf_counter() - t0
+
+    t1 = run(1)                                          # one image calibrates the sample size
+    images = int(max(1, min(c["images"], target_seconds / max(t1, 1e-3))))
+    t = run(images)
+    flops = 2.0 * images * rows_per_image * c["N"] * c["K"]
+    return flops / t / 1e12, orc.num_threads(), f"{images} of {c['images']} images ({images * rows_per_image} rows) of {cfg_name}", t
+
+
+def reference_arm(args, rank: int, world: int) -> None:
+    if rank != 0:
+        return
+    from siglip_b200 import synth
+    c = synth.CONFIGS[args.config]
+    vals = []
+    sample = ""
+    cores = 0
+    per_step_target = max(1.0, min(10.0, 60.0 / max(1, args.steps + args.warmup)))
+    for i in range(args.warmup + args.steps):
+        v, cores, sample, _t = cpu_oracle_rate(args.config, per_step_target)
+        if i >= args.warmup:
+            vals.append(v)
+    value = sum(vals) / len(vals)
+    flops = 2.0 * c["M"] * c["N"] * c["K"]
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": flops / (value * 1e12) * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.config),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference project is CUDA-only; this arm times the CPU restatement of its algorithm "
+                "(FP32-accumulate GEMM over dequantised e4m3 + fused epilogue) on the host cores; "
+                "ms_per_step is the full workload at the measured rate",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(name: str) -> dict:
+    from siglip_b200 import synth
+    c = synth.CONFIGS[name]
+    op = {0: "patch-embed + periodic table add", 1: "FC1 + bias + GELU(tanh)", 2: "FC2 + bias + residual"}[c["op"]]
+    return {"workload": f"SigLIP {name}: {op}, M={c['M']} ({c['images']} images) K={c['K']} N={c['N']}, "
+                        "e4m3 x e4m3 -> fp32 accumulate -> bf16, per-tensor scales",
+            "per_gpu_rows": c["M"], "l2": "three operand sets rotated per step (working set > 126 MB L2)"}
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def launch_fn(eng, p, dev):
+    """Returns (callable(i) launching one step on operand set i, number of sets, list of outputs)."""
+    from siglip_b200 import synth
+    sa = torch.tensor([p.scale_a], device=dev)
+    sb = torch.tensor([p.scale_b], device=dev)
+    sets = 3
+    As = [p.A] + [p.A.clone() for _ in range(sets - 1)]
+    Ds = [torch.empty((p.M, p.N), dtype=torch.bfloat16, device=dev) for _ in range(sets)]
+    if p.op == synth.OP_FC1_GELU:
+        return (lambda i: eng.fc1_gelu(As[i % sets], p.B, p.bias, scale_a=sa, scale_b=sb, out=Ds[i % sets])), sets, Ds
+    if p.op == synth.OP_FC2_RESIDUAL:
+        Rs = [p.residual] + [p.residual.clone() for _ in range(sets - 1)]
+        return (lambda i: eng.fc2_residual(As[i % sets], p.B, p.bias, Rs[i % sets], scale_a=sa, scale_b=sb,
+                                           out=Ds[i % sets])), sets, Ds
+    return (lambda i: eng.patch_embed(As[i % sets], p.B, p.table, scale_a=sa, scale_b=sb, out=Ds[i % sets])), sets, Ds
+
+
+def time_steps(fn, steps: int, warmup: int, barrier) -> float:
+    """ms per step: `warmup` untimed steps, then `steps` timed ones between two CUDA events on the
+    stream the kernels are launched on, a barrier and a device synchronise on both sides."""
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    return e0.elapsed_time(e1) / steps
+
+
+def layer_table(eng, dev, steps: int, peaks: dict) -> dict:
+    """Per-layer numbers for the other configurations (C1, C3, C4), same timing protocol."""
+    from siglip_b200 import synth
+    out = {}
+    for name in ("C1", "C3", "C4"):
+        p = synth.make_config(name, seed=0, device=dev)
+        fn, _, _ = launch_fn(eng, p, dev)
+        ms = time_steps(fn, steps, 3, lambda: None)
+        eng.device_status()
+        tf = p.flops() / ms / 1e9
+        gbs = p.min_bytes() / ms / 1e6
+        out[name] = {"ms": ms, "tflops": tf, "gbs": gbs, "frac_fp8_measured": tf / (2 * peaks["bf16_tflops"]),
+                     "frac_hbm_measured": gbs / peaks["hbm_gbs"], "frac_fp8_nominal_4500": tf / 4500.0,
+                     "images_per_s": synth.CONFIGS[name]["images"] / ms * 1e3}
+        del p, fn
+        torch.cuda.empty_cache()
+    return out
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="C2", choices=["C1", "C2", "C3", "C4"])
+    ap.add_argument("--layers", action="store_true", help="also time C1, C3 and C4 and add them under 'layers'")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--variant", type=int, default=-1, help="force a kernel variant (sweeps)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        reference_arm(args, rank, world)
+        return
+
+    import torch.distributed as dist
+    from siglip_b200 import Engine, synth
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: there is no CPU fallback for the hot path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        barrier = lambda: dist.barrier()
+    else:
+        barrier = lambda: None
+
+    peaks = measured_peaks()
+    eng = Engine(local_rank)
+    if args.variant >= 0:
+        eng.set_variant(args.variant)
+    p = synth.make_config(args.config, seed=rank, device=dev)
+    fn, _, Ds = launch_fn(eng, p, dev)
+    out_bytes = p.M * p.N * 2
+
+    sampler = ClockSampler(local_rank)
+    for i in range(args.warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    barrier()
+    eng.device_status()
+    ms = e0.elapsed_time(e1) / args.steps
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t)
+    flops = p.flops()
+    value = world * flops / ms_max / 1e9                      # TFLOP/s, all ranks
+
+    # ---- end to end: pinned host operands through the *_host entry point
+    A_h = torch.zeros((p.M, p.A.stride(0)), dtype=torch.uint8).pin_memory()[:, :p.K]
+    A_h.copy_(p.A)
+    B_h = p.B.cpu().pin_memory()
+    D_h = torch.empty((p.M, p.N), dtype=torch.bfloat16).pin_memory()
+    side_h = None
+    if p.op == synth.OP_FC1_GELU:
+        bias_h = p.bias.cpu().pin_memory()
+        e2e_fn = lambda: eng.fc1_gelu_host(A_h, B_h, bias_h, D_h, scale_a=p.scale_a, scale_b=p.scale_b)
+        side_bytes = bias_h.numel() * 2
+    elif p.op == synth.OP_FC2_RESIDUAL:
+        bias_h = p.bias.cpu().pin_memory()
+        side_h = p.residual.cpu().pin_memory()
+        e2e_fn = lambda: eng.fc2_residual_host(A_h, B_h, bias_h, side_h, D_h, scale_a=p.scale_a, scale_b=p.scale_b)
+        side_bytes = bias_h.numel() * 2 + side_h.numel() * 2
+    else:
+        side_h = p.table.cpu().pin_memory()
+        e2e_fn = lambda: eng.patch_embed_host(A_h, B_h, side_h, D_h, scale_a=p.scale_a, scale_b=p.scale_b)
+        side_bytes = side_h.numel() * 2
+    e2e_steps = max(3, min(args.steps, 10))
+    e2e_fn()
+    torch.cuda.synchronize()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_fn()                                              # blocking: returns when D is in host memory
+    e2e_ms = (time.perf_counter() - t0) / e2e_steps * 1e3
+    barrier()
+    t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_value = world * flops / float(t) / 1e9
+    same = torch.equal(D_h.to(dev).view(torch.uint16), Ds[0].view(torch.uint16)) if rank == 0 else True
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_max, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "e4m3 x e4m3 -> f32", "data": "synthetic", "config": workload_config(args.config),
+            "clocks": clocks, "gpu_launches": args.steps,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(p.M * p.A.stride(0) + p.N * p.B.stride(0) + side_bytes + 12),
+                    "d2h_bytes_per_step": int(out_bytes), "ms_per_step": float(t), "steps": e2e_steps,
+                    "matches_device_path": bool(same)},
+            "images_per_s": world * synth.CONFIGS[args.config]["images"] / ms_max * 1e3,
+            "kernel_config": eng.query_config(p.op, p.M, p.N, p.K),
+        }
+        tensor_bound = p.op != synth.OP_PATCH_EMBED
+        per_gpu_tf = flops / ms / 1e9
+        per_gpu_gbs = p.min_bytes() / ms / 1e6
+        if tensor_bound:
+            peak = 2.0 * peaks["bf16_tflops"]
+            line["roofline"] = {"bound": "tensor", "achieved": per_gpu_tf, "peak": peak, "unit": "TFLOP/s",
+                                "frac": per_gpu_tf / peak, "traffic": None,
+                                "peak_source": f"2 x bf16 burst GEMM rate of {peaks['source']} MEASURED_PEAKS (e4m3 MMA rate is twice bf16)",
+                                "frac_of_nominal_4500": per_gpu_tf / 4500.0,
+                                "hbm_gbs_algorithmic": per_gpu_gbs}
+        else:
+            line["roofline"] = {"bound": "hbm", "achieved": per_gpu_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                "frac": per_gpu_gbs / peaks["hbm_gbs"], "traffic": None,
+                                "peak_source": f"{peaks['source']} copy bandwidth", "tflops": per_gpu_tf}
+        if not args.no_cpu_baseline:
+            v, cores, sample, secs = cpu_oracle_rate(args.config, args.cpu_seconds)
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
+                                    "seconds": secs}
+        if args.layers:
+            line["layers"] = layer_table(eng, dev, max(20, min(args.steps, 100)), peaks)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,218 @@
+"""Parity of the CUDA path (through the C ABI of libsiglip_fp8.so) with the CPU oracle.
+
+Shapes cover every tail the kernels have to handle (M not a multiple of 128 / 256, N not a
+multiple of the tile width, K not a multiple of 128 or 32, K = 588 with a 592-byte pitch,
+the period wrap of the positional table) on seeded random operands, for the variant the
+dispatch table picks and for every compiled variant; plus the reference's constant-operand
+known answers.
+"""
+import numpy as np
+import pytest
+import torch
+
+from siglip_b200 import synth
+from siglip_b200.layers import num_variants, describe_variant
+from tests.tolerance import check_bf16, check_e4m3
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def dscalar(x):
+    return torch.tensor([x], dtype=torch.float32, device=DEV)
+
+
+def bits(t: torch.Tensor) -> np.ndarray:
+    return t.view(torch.uint16).cpu().numpy()
+
+
+def run_fc1(engine, oracle, M, N, K, seed, e4m3=False, out_scale=0.01, flags_f32_bias=False):
+    p = synth.make_fc1(M, N, K, seed=seed, device=DEV)
+    bias = p.bias.float() if flags_f32_bias else p.bias
+    kw = dict(scale_a=dscalar(p.scale_a), scale_b=dscalar(p.scale_b))
+    A, B = p.A.cpu().numpy(), p.B.cpu().numpy()
+    bias_np = bias.cpu().numpy() if flags_f32_bias else bits(bias)
+    fl = 1 if flags_f32_bias else 0
+    if e4m3:
+        D = engine.fc1_gelu(p.A, p.B, bias, out_dtype=torch.uint8, out_scale=dscalar(out_scale), **kw)
+        engine.device_status()
+        ref = oracle.fc1_gelu(A, B, p.scale_a, p.scale_b, bias_np, out_e4m3=True, out_scale=out_scale, flags=fl)
+        return check_e4m3(D.cpu().numpy(), ref, f"fc1-e4m3 {M}x{N}x{K}")
+    D = engine.fc1_gelu(p.A, p.B, bias, **kw)
+    engine.device_status()
+    ref = oracle.fc1_gelu(A, B, p.scale_a, p.scale_b, bias_np, flags=fl)
+    return check_bf16(bits(D), ref, f"fc1 {M}x{N}x{K}")
+
+
+def run_fc2(engine, oracle, M, N, K, seed):
+    p = synth.make_fc2(M, N, K, seed=seed, device=DEV)
+    D = engine.fc2_residual(p.A, p.B, p.bias, p.residual, scale_a=dscalar(p.scale_a), scale_b=dscalar(p.scale_b))
+    engine.device_status()
+    ref = oracle.fc2_residual(p.A.cpu().numpy(), p.B.cpu().numpy(), p.scale_a, p.scale_b, bits(p.bias), bits(p.residual))
+    return check_bf16(bits(D), ref, f"fc2 {M}x{N}x{K}")
+
+
+def run_pe(engine, oracle, M, N, K, period, seed, row_phase=0, f32_add=False):
+    p = synth.make_patch_embed(M, N, K, period, seed=seed, device=DEV, pixels=True)
+    fl = 2 if f32_add else 0
+    D = engine.patch_embed(p.A, p.B, p.table, scale_a=dscalar(p.scale_a), scale_b=dscalar(p.scale_b),
+                           row_phase=row_phase, flags=fl)
+    engine.device_status()
+    ref = oracle.patch_embed(p.A.cpu().numpy(), p.B.cpu().numpy(), p.scale_a, p.scale_b, bits(p.table),
+                             row_phase=row_phase, flags=fl)
+    return check_bf16(bits(D), ref, f"pe {M}x{N}x{K} period {period}")
+
+
+TAIL_SHAPES = [
+    (1, 16, 32), (31, 208, 76), (127, 16, 588), (128, 256, 128), (129, 272, 160), (255, 1152, 588),
+    (257, 464, 1152), (729, 4304, 96), (300, 1152, 4304), (1000, 768, 768),
+]
+
+
+@pytest.fixture(autouse=True)
+def _default_variant(engine):
+    engine.set_variant(-1)
+    yield
+    engine.set_variant(-1)
+
+
+@pytest.mark.parametrize("M,N,K", TAIL_SHAPES)
+def test_fc1_tails(engine, oracle, M, N, K):
+    run_fc1(engine, oracle, M, N, K, seed=M + N + K)
+
+
+@pytest.mark.parametrize("M,N,K", TAIL_SHAPES)
+def test_fc2_tails(engine, oracle, M, N, K):
+    run_fc2(engine, oracle, M, N, K, seed=M + N + K + 1)
+
+
+@pytest.mark.parametrize("M,N,K", TAIL_SHAPES)
+def test_patch_embed_tails(engine, oracle, M, N, K):
+    run_pe(engine, oracle, M, N, K, period=196, seed=M + N + K + 2, row_phase=(M * 7) % 196)
+
+
+@pytest.mark.parametrize("M,N,K", [(129, 272, 160), (729, 4304, 96), (257, 256, 1152)])
+def test_fc1_e4m3_output(engine, oracle, M, N, K):
+    run_fc1(engine, oracle, M, N, K, seed=11, e4m3=True)
+
+
+def test_fc1_fp32_bias(engine, oracle):
+    run_fc1(engine, oracle, 300, 464, 588, seed=5, flags_f32_bias=True)
+
+
+def test_patch_embed_fp32_add_mode(engine, oracle):
+    run_pe(engine, oracle, 500, 768, 588, period=196, seed=6, row_phase=3, f32_add=True)
+
+
+def test_patch_embed_period_wrap(engine, oracle):
+    """Rows 195 / 196 / 197 and a period that is not a multiple of 32 (729)."""
+    run_pe(engine, oracle, 3 * 729 + 5, 1152, 588, period=729, seed=8)
+
+
+@pytest.mark.parametrize("vid", range(11))
+def test_every_variant(engine, oracle, vid):
+    assert vid < num_variants()
+    engine.set_variant(vid)
+    cfg = describe_variant(vid)
+    M = 2 * cfg["tile_m"] + 77
+    run_fc1(engine, oracle, M, 464, 588, seed=20 + vid)
+    run_fc1(engine, oracle, M, 464, 588, seed=20 + vid, e4m3=True)
+    run_fc2(engine, oracle, M, 1152, 300, seed=40 + vid)
+    run_pe(engine, oracle, M, 784, 588, period=196, seed=60 + vid, row_phase=9)
+
+
+def test_multi_wave_determinism(engine, oracle):
+    """More tiles than SMs (several rounds of the persistent loop and both TMEM buffers), twice: bit-equal runs."""
+    p = synth.make_fc1(6000, 2304, 1152, seed=3, device=DEV)
+    kw = dict(scale_a=dscalar(p.scale_a), scale_b=dscalar(p.scale_b))
+    D1 = engine.fc1_gelu(p.A, p.B, p.bias, **kw)
+    D2 = engine.fc1_gelu(p.A, p.B, p.bias, **kw)
+    engine.device_status()
+    assert torch.equal(D1.view(torch.uint16), D2.view(torch.uint16))
+    ref = oracle.fc1_gelu(p.A.cpu().numpy(), p.B.cpu().numpy(), p.scale_a, p.scale_b, bits(p.bias))
+    check_bf16(bits(D1), ref, "fc1 6000x2304x1152")
+
+
+def test_output_guard_bands(engine, oracle):
+    """A padded output (ldd > N) with sentinels around it: nothing outside [M, N] may be written."""
+    M, N, K, ldd = 333, 464, 588, 512
+    p = synth.make_fc1(M, N, K, seed=9, device=DEV)
+    buf = torch.full((M + 64, ldd), -7.0, dtype=torch.bfloat16, device=DEV)
+    out = buf[32:32 + M, :N]
+    engine.fc1_gelu(p.A, p.B, p.bias, scale_a=dscalar(p.scale_a), scale_b=dscalar(p.scale_b), out=out)
+    engine.device_status()
+    assert bool((buf[:32] == -7.0).all()) and bool((buf[32 + M:] == -7.0).all()) and bool((buf[:, N:] == -7.0).all())
+    ref = oracle.fc1_gelu(p.A.cpu().numpy(), p.B.cpu().numpy(), p.scale_a, p.scale_b, bits(p.bias))
+    check_bf16(bits(out.contiguous()), ref, "fc1 guard bands")
+
+
+def test_reference_known_answers_on_gpu(engine):
+    """The reference's constant operands and closed forms (patch_embed.cu:121-145,273-306;
+    fc1_gelu.cu:200-225; fc2.cu:231-259) at its own N and K, bit for bit."""
+    M = 5 * 196 + 17
+    ones = lambda n, k: torch.full((n, k), 0x3C, dtype=torch.uint8, device=DEV)
+    def weights(n, k):
+        w = ones(n, k)
+        w[1::2] = 0x38
+        return w
+    # patch-embed 768 x 768
+    N, K = 768, 768
+    bias = torch.arange(1, N + 1, dtype=torch.float32, device=DEV)
+    pos = (3.0 * (torch.arange(196, dtype=torch.float32, device=DEV) + 1))[:, None].expand(196, N)
+    table = (bias[None, :] + pos).to(torch.bfloat16).contiguous()
+    D = engine.patch_embed(ones(M, K), weights(N, K), table)
+    acc = torch.where(torch.arange(N, device=DEV) % 2 == 1, 1.0, 1.5) * (K * 1.5)
+    rows = torch.arange(M, device=DEV) % 196
+    expect = (acc.to(torch.bfloat16).float()[None, :] + table.float()[rows]).to(torch.bfloat16)
+    assert torch.equal(D, expect)
+    # FC1 768 -> 3072: gelu(x) == x for x this large
+    N, K = 3072, 768
+    bias = torch.arange(1, N + 1, dtype=torch.float32, device=DEV)
+    D = engine.fc1_gelu(ones(M, K), weights(N, K), bias)
+    acc = torch.where(torch.arange(N, device=DEV) % 2 == 1, 1.0, 1.5) * (K * 1.5)
+    assert torch.equal(D, (acc + bias).to(torch.bfloat16)[None, :].expand(M, N))
+    # FC2 3072 -> 768
+    N, K = 768, 3072
+    bias = torch.arange(1, N + 1, dtype=torch.float32, device=DEV)
+    r = (torch.arange(M, device=DEV) % 128).float()[:, None] * 0.25 + torch.arange(N, device=DEV).float()[None, :] * 0.125
+    residual = r.to(torch.bfloat16)
+    D = engine.fc2_residual(ones(M, K), weights(N, K), bias, residual)
+    acc = torch.where(torch.arange(N, device=DEV) % 2 == 1, 1.0, 1.5) * (K * 1.5)
+    assert torch.equal(D, ((acc + bias)[None, :] + residual.float()).to(torch.bfloat16))
+    engine.device_status()
+
+
+def test_argument_validation(engine):
+    import siglip_b200.lib as L
+    A = torch.zeros((64, 128), dtype=torch.uint8, device=DEV)
+    B = torch.zeros((40, 128), dtype=torch.uint8, device=DEV)        # N = 40 is not a multiple of 16
+    with pytest.raises(L.SL8Error) as e:
+        engine.fc1_gelu(A, B, None)
+    assert e.value.code == L.SL8_ERR_UNSUPPORTED
+    B = torch.zeros((48, 128), dtype=torch.uint8, device=DEV)
+    Abad = torch.zeros((64, 136), dtype=torch.uint8, device=DEV)[:, :128]   # pitch 136 is not a multiple of 16
+    with pytest.raises(L.SL8Error) as e:
+        engine.fc1_gelu(Abad, B, None)
+    assert e.value.code == L.SL8_ERR_ALIGNMENT
+    Aoff = torch.zeros((64 * 128 + 16,), dtype=torch.uint8, device=DEV)[8:8 + 64 * 128].view(64, 128)
+    with pytest.raises(L.SL8Error) as e:
+        engine.fc1_gelu(Aoff, B, None)
+    assert e.value.code == L.SL8_ERR_ALIGNMENT
+    out = engine.fc1_gelu(A, B, None)                                 # a valid call still works afterwards
+    engine.device_status()
+    assert out.shape == (64, 48) and bool((out == 0).all())
+
+
+def test_host_operand_entry_points(engine, oracle):
+    """The *_host calls (pinned host buffers, slabs pipelined over three streams)."""
+    M, N, K = 70000, 464, 588          # several slabs
+    p = synth.make_fc1(M, N, K, seed=13, device="cpu")
+    A = torch.empty((M, synth.pitch16(K)), dtype=torch.uint8).pin_memory()
+    A[:, :K] = p.A
+    out = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    engine.fc1_gelu_host(A[:, :K], p.B, p.bias, out, scale_a=p.scale_a, scale_b=p.scale_b)
+    engine.device_status()
+    rows = np.r_[0:300, 33000:33300, M - 300:M]
+    ref = oracle.fc1_gelu(np.ascontiguousarray(p.A.numpy()[rows]), p.B.numpy(), p.scale_a, p.scale_b, bits(p.bias))
+    check_bf16(out.view(torch.uint16).numpy()[rows], ref, "fc1 host operands")
