@@ -176,7 +176,12 @@ def launch_fn(eng, p, dev):
     sa = torch.tensor([p.scale_a], device=dev)
     sb = torch.tensor([p.scale_b], device=dev)
     sets = 3
-    As = [p.A] + [p.A.clone() for _ in range(sets - 1)]
+
+    def clone_pitched(t):                       # keeps the 16-byte row pitch of a K = 588 operand
+        c = torch.empty_strided(t.shape, t.stride(), dtype=t.dtype, device=t.device)
+        return c.copy_(t)
+
+    As = [p.A] + [clone_pitched(p.A) for _ in range(sets - 1)]
     Ds = [torch.empty((p.M, p.N), dtype=torch.bfloat16, device=dev) for _ in range(sets)]
     if p.op == synth.OP_FC1_GELU:
         return (lambda i: eng.fc1_gelu(As[i % sets], p.B, p.bias, scale_a=sa, scale_b=sb, out=Ds[i % sets])), sets, Ds

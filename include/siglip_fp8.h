@@ -205,6 +205,24 @@ int sl8_device_status(sl8_handle_t h, sl8_stream_t stream, unsigned detail[4]);
 /* Wait budget in milliseconds for later launches on this handle (default 2000). */
 int sl8_set_wait_budget_ms(sl8_handle_t h, int ms);
 
+/* ---- in-kernel tracing ------------------------------------------------------------------
+ * Counterpart of the reference's -DTIMING build (clock64 stamps in the MMA thread and the
+ * epilogue warps, kernel_body.cuh:523-537,569-636,695-750; host read-back print_timing
+ * kernel_body.cuh:821-1001), switchable at run time instead of by recompiling.
+ * sl8_trace_enable(h, 1) allocates a device buffer (the one allocation outside sl8_create;
+ * not on the call path of a layer); later launches on the handle then record, per CTA,
+ * SL8_TRACE_SLOTS clock-cycle totals of the LAST launch:
+ *   [0] TMA producer waiting for a free stage   [1] producer total
+ *   [2] MMA thread waiting for operands         [3] MMA thread waiting for a free accumulator
+ *   [4] MMA thread total                        [5] epilogue warp 0 waiting for an accumulator
+ *   [6] epilogue warp 0 total                   [7] epilogue warp 0 waiting for staging to drain
+ *   [8] tiles of this CTA pair                  [9] epilogue warp 0 waiting for tcgen05.ld
+ * sl8_trace_read synchronises the device and copies min(grid of the last launch, max_blocks)
+ * records into out[max_blocks * SL8_TRACE_SLOTS]; returns the number of records or an error. */
+#define SL8_TRACE_SLOTS 16
+int sl8_trace_enable(sl8_handle_t h, int on);
+int sl8_trace_read(sl8_handle_t h, long long* out, int max_blocks);
+
 #ifdef __cplusplus
 }
 #endif

@@ -65,6 +65,9 @@ struct sl8_context {
     int device = 0;
     int sm_count = 0;
     uint32_t* d_status = nullptr;       // 4 words
+    long long* d_prof = nullptr;        // tracing buffer, PROF_SLOTS per CTA, or null
+    int prof_blocks = 0;
+    int last_grid = 0;
     encode_tiled_fn encode = nullptr;
     int forced_variant = -1;
     unsigned wait_budget_ms = 2000;
@@ -107,15 +110,17 @@ struct DeviceGuard {
 int pick_variant(int op, int out_dtype, long long M, int N, int K) {
     (void)out_dtype;
     (void)K;
+    (void)N;
     const long long tiles256 = ((M + 255) / 256) * ((N + 255) / 256);
     if (tiles256 < 74) {
         // Too few 256 x 256 tiles to fill the GPU: smaller tiles give more of the 148 SMs work.
         return (M <= 128) ? 8 : 9;
     }
-    if (op == SL8_OP_FC2_RESIDUAL || op == SL8_OP_PATCH_EMBED) {
-        // N = 1152 is 6 x 192 exactly; 256-wide tiles would waste 10 % of the MMAs.
-        if (N % 256 != 0 && N % 192 == 0) return 6;
-    }
+    // A tcgen05.mma of a CTA pair takes about 150 cycles whatever its N (measured for N = 128, 192,
+    // 256), so the widest tile does the most work per instruction even where N = 1152 leaves the
+    // fifth 256-wide tile half empty.
+    if (op == SL8_OP_FC1_GELU) return 4;   // GELU epilogue: two epilogue warps per scheduler
+    if (op == SL8_OP_PATCH_EMBED) return 4;
     return 3;
 }
 
@@ -143,7 +148,7 @@ int validate(sl8_handle_t h, const Problem& q) {
     if (q.M > 0x7FFFFF00ll) return fail(h, SL8_ERR_UNSUPPORTED, "M exceeds 2^31 rows");
     if (q.out_dtype != SL8_OUT_BF16 && q.out_dtype != SL8_OUT_E4M3)
         return fail(h, SL8_ERR_INVALID_VALUE, "unknown out_dtype");
-    if (q.flags & ~(unsigned)(SL8_FLAG_BIAS_F32 | SL8_FLAG_PE_F32_ADD)) return fail(h, SL8_ERR_INVALID_VALUE, "unknown flag bits");
+    if (q.flags & ~(unsigned)(SL8_FLAG_BIAS_F32 | SL8_FLAG_PE_F32_ADD | 0xFF00u)) return fail(h, SL8_ERR_INVALID_VALUE, "unknown flag bits");
     if (q.N % 16 != 0) return fail(h, SL8_ERR_UNSUPPORTED, "N must be a multiple of 16");
     if (q.lda < q.K || q.ldb < q.K) return fail(h, SL8_ERR_INVALID_VALUE, "lda / ldb smaller than K");
     if (q.ldd < q.N) return fail(h, SL8_ERR_INVALID_VALUE, "ldd smaller than N");
@@ -282,8 +287,11 @@ int run(sl8_handle_t h, const Problem& q, cudaStream_t stream) {
     p.flags = q.flags;
     p.wait_budget_ms = h->wait_budget_ms;
     p.status = h->d_status;
+    p.prof = h->d_prof;
 
     const int grid = grid_for(h, v, slot, p.num_tiles);
+    h->last_grid = grid;
+    if (h->d_prof && grid > h->prof_blocks) return fail(h, SL8_ERR_INVALID_VALUE, "tracing buffer smaller than the grid");
     cudaError_t e = v->launch[slot](&map_a, &map_b, &map_d, &p, grid, stream);
     if (e != cudaSuccess) return fail_cuda(h, e, "kernel launch");
     return SL8_OK;
@@ -382,6 +390,7 @@ SL8_API int sl8_destroy(sl8_handle_t h) {
         if (pp.d_scales) cudaFree(pp.d_scales);
         if (pp.h_scales) cudaFreeHost(pp.h_scales);
         if (h->d_status) cudaFree(h->d_status);
+        if (h->d_prof) cudaFree(h->d_prof);
         (void)cudaGetLastError();
     }
     delete h;
@@ -635,4 +644,37 @@ SL8_API int sl8_set_wait_budget_ms(sl8_handle_t h, int ms) {
     if (!h || ms < 1) return SL8_ERR_INVALID_VALUE;
     h->wait_budget_ms = static_cast<unsigned>(ms);
     return SL8_OK;
+}
+
+// =========================================================================== tracing
+
+SL8_API int sl8_trace_enable(sl8_handle_t h, int on) {
+    if (!h) return SL8_ERR_INVALID_VALUE;
+    std::lock_guard<std::mutex> lock(h->mu);
+    DeviceGuard guard(h->device);
+    if (on && !h->d_prof) {
+        const int blocks = 2 * h->sm_count;
+        cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&h->d_prof), sizeof(long long) * sl8::PROF_SLOTS * blocks);
+        if (e != cudaSuccess) return fail_cuda(h, e, "cudaMalloc(tracing buffer)");
+        cudaMemset(h->d_prof, 0, sizeof(long long) * sl8::PROF_SLOTS * blocks);
+        h->prof_blocks = blocks;
+    } else if (!on && h->d_prof) {
+        cudaDeviceSynchronize();
+        cudaFree(h->d_prof);
+        h->d_prof = nullptr;
+        h->prof_blocks = 0;
+    }
+    return SL8_OK;
+}
+
+SL8_API int sl8_trace_read(sl8_handle_t h, long long* out, int max_blocks) {
+    if (!h || !out || max_blocks < 1) return SL8_ERR_INVALID_VALUE;
+    if (!h->d_prof) return fail(h, SL8_ERR_INVALID_VALUE, "tracing is not enabled");
+    DeviceGuard guard(h->device);
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return fail_cuda(h, e, "cudaDeviceSynchronize");
+    int n = h->last_grid < max_blocks ? h->last_grid : max_blocks;
+    e = cudaMemcpy(out, h->d_prof, sizeof(long long) * sl8::PROF_SLOTS * n, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail_cuda(h, e, "read of the tracing buffer");
+    return n;
 }

@@ -36,7 +36,9 @@ namespace sl8 {
 
 enum : int { OP_PE = 0, OP_FC1 = 1, OP_FC2 = 2 };
 enum : int { OUT_BF16 = 0, OUT_E4M3 = 1 };
-enum : unsigned { FLAG_BIAS_F32 = 1u, FLAG_PE_F32_ADD = 2u };
+enum : unsigned { FLAG_BIAS_F32 = 1u, FLAG_PE_F32_ADD = 2u,
+                  DBG_SKIP_SIDE = 0x100u, DBG_SKIP_GELU = 0x200u, DBG_SKIP_BIAS = 0x400u, DBG_SKIP_STORE = 0x800u,
+                  DBG_SKIP_LOAD = 0x1000u, DBG_SKIP_EPILOGUE = 0x2000u };
 
 // status[0] codes: which role gave up.
 enum : uint32_t {
@@ -45,6 +47,21 @@ enum : uint32_t {
     ST_MMA_FULL_WAIT = 2,
     ST_MMA_TMEM_EMPTY_WAIT = 3,
     ST_EPI_TMEM_FULL_WAIT = 4
+};
+
+// Tracing slots written per CTA when KernelParams::prof is set (cycles, clock64).
+enum : int {
+    PROF_PRODUCER_WAIT = 0,   // TMA producer waiting for a free stage
+    PROF_PRODUCER_TOTAL = 1,
+    PROF_MMA_WAIT_FULL = 2,   // MMA thread waiting for operands
+    PROF_MMA_WAIT_TMEM = 3,   // MMA thread waiting for a free accumulator
+    PROF_MMA_TOTAL = 4,
+    PROF_EPI_WAIT_ACC = 5,    // epilogue warp 0 waiting for a finished accumulator
+    PROF_EPI_TOTAL = 6,
+    PROF_EPI_WAIT_STORE = 7,  // epilogue warp 0 waiting for staging to drain
+    PROF_TILES = 8,
+    PROF_EPI_WAIT_LD = 9,     // epilogue warp 0 waiting for tcgen05.ld
+    PROF_SLOTS = 16
 };
 
 struct KernelParams {
@@ -68,6 +85,7 @@ struct KernelParams {
     unsigned flags;
     unsigned wait_budget_ms;
     uint32_t* status;                // 4 words: code, barrier/stage, tile, block
+    long long* prof;                 // optional: PROF_SLOTS clock64 totals per CTA (null = tracing off)
 };
 
 template <int CG, int TN, int STAGES, int EPI_WARPS, int OUT, bool TMA_STORE>
@@ -86,11 +104,15 @@ struct KernelTraits {
     static constexpr int OUT_BYTES = (OUT == OUT_BF16) ? 2 : 1;
     static constexpr int REGION_COLS = 128 / OUT_BYTES;          // output columns in one 128-byte staging row
     static constexpr int REGION_BYTES = 32 * 128;                // 32 rows of one warp
-    static constexpr int STAGING_BYTES = TMA_STORE ? EPI_WARPS * 2 * REGION_BYTES : 0;
+    // Staging buffers per epilogue warp: two (write one while TMA reads the other) with one warp
+    // per scheduler; one where a second warp on the same scheduler covers the wait instead.
+    static constexpr int STAGING_BUFS = (EPI_WARPS == 8) ? 1 : 2;
+    static constexpr int STAGING_BYTES = TMA_STORE ? EPI_WARPS * STAGING_BUFS * REGION_BYTES : 0;
     static constexpr int COLS_PER_WARP = TN / (EPI_WARPS / 4);   // columns one epilogue warp covers
+    static constexpr int BIAS_BYTES = EPI_WARPS * COLS_PER_WARP * 4;   // fp32 bias of the current tile, one copy per warp
     static constexpr int THREADS = (2 + EPI_WARPS) * 32;
     static constexpr int BAR_BYTES = 256;
-    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STAGING_BYTES + BAR_BYTES;
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STAGING_BYTES + BIAS_BYTES + BAR_BYTES;
     static_assert(STAGE_BYTES % 1024 == 0, "every operand tile must start on a swizzle-atom boundary");
     static_assert(COLS_PER_WARP % REGION_COLS == 0 || !TMA_STORE, "a warp stores whole staging regions");
     static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB a CTA may use");
@@ -152,33 +174,43 @@ __device__ __forceinline__ void unpack8_bf16(const uint4& q, float (&f)[8]) {
 struct EpiRow {
     float scale;                   // scale_a * scale_b
     float inv_out;                 // 1 / out_scale
-    const uint8_t* bias;           // byte pointer to bias[0] or null
     const __nv_bfloat16* side_row; // this lane's table / residual row, or null when the row is past M
     uint8_t* out_row;              // this lane's output row (direct stores), or null when past M
-    uint32_t stage_row;            // shared address of this lane's 128-byte staging row (TMA stores)
+    uint32_t stage_row;            // byte offset of this lane's 128-byte staging row (TMA stores)
     uint32_t swz;                  // (lane & 7): XOR applied to the 16-byte chunk index
     unsigned flags;
 };
 
-// Transforms 16 accumulator columns (v[16*H .. 16*H+15] = columns col .. col+15 of this
-// lane's row) and stores them.  `chunk16` is the index of the first 16-byte piece inside
-// the staging row when TMA stores are used.
+// 32 bf16 side values (table or residual) of one 32-column chunk of this lane's row; columns at
+// or past N are not read.
+__device__ __forceinline__ void load_side32(uint4 (&s)[4], const __nv_bfloat16* side_row, int col, int N) {
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        if (side_row != nullptr && col + 16 * h < N) {
+            s[2 * h + 0] = __ldg(reinterpret_cast<const uint4*>(side_row + col + 16 * h));
+            s[2 * h + 1] = __ldg(reinterpret_cast<const uint4*>(side_row + col + 16 * h + 8));
+        } else {
+            s[2 * h + 0] = make_uint4(0, 0, 0, 0);
+            s[2 * h + 1] = make_uint4(0, 0, 0, 0);
+        }
+    }
+}
+
+// Transforms 16 accumulator columns (v[16*H .. 16*H+15] = columns col .. col+15 of this lane's row)
+// and stores them.  bias16 points at the 16 fp32 bias values of these columns in shared memory
+// (FC1 / FC2); side holds their 16 bf16 table / residual values (patch-embed / FC2).  `chunk16`
+// is the index of the first 16-byte piece inside the staging row when TMA stores are used.
 template <int OP, int OUT, bool TMA_STORE, int H>
-__device__ __forceinline__ void epilogue_16(const float (&v)[32], const EpiRow& e, int col, uint32_t region_base,
+__device__ __forceinline__ void epilogue_16(const float (&v)[32], const EpiRow& e, const float* bias16,
+                                            const uint4& side_lo, const uint4& side_hi, int col, uint32_t region_base,
                                             int chunk16) {
     float x[16];
-#pragma unroll
-    for (int i = 0; i < 16; i++) x[i] = v[16 * H + i] * e.scale;
-
     uint32_t w[8];  // bf16: 8 words (16 values); e4m3: 4 words used
 
     if constexpr (OP == OP_PE) {
-        uint4 t0 = make_uint4(0, 0, 0, 0), t1 = make_uint4(0, 0, 0, 0);
-        if (e.side_row != nullptr) {
-            t0 = __ldg(reinterpret_cast<const uint4*>(e.side_row + col));
-            t1 = __ldg(reinterpret_cast<const uint4*>(e.side_row + col + 8));
-        }
-        const uint32_t tw[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
+#pragma unroll
+        for (int i = 0; i < 16; i++) x[i] = v[16 * H + i] * e.scale;
+        const uint32_t tw[8] = {side_lo.x, side_lo.y, side_lo.z, side_lo.w, side_hi.x, side_hi.y, side_hi.z, side_hi.w};
         if (e.flags & FLAG_PE_F32_ADD) {
 #pragma unroll
             for (int i = 0; i < 8; i++)
@@ -189,39 +221,29 @@ __device__ __forceinline__ void epilogue_16(const float (&v)[32], const EpiRow& 
             for (int i = 0; i < 8; i++) w[i] = add_bf16x2(pack_bf16x2(x[2 * i], x[2 * i + 1]), tw[i]);
         }
     } else {
-        // bias (same address in every lane: served as a broadcast)
-        if (e.bias != nullptr) {
-            if (e.flags & FLAG_BIAS_F32) {
-                const float4* bp = reinterpret_cast<const float4*>(e.bias + static_cast<size_t>(col) * 4);
+        // acc * scale + bias in one FMA; the bias comes from shared memory, the same address in every
+        // lane (a broadcast read).
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const float4 b = __ldg(bp + i);
-                    x[4 * i + 0] += b.x; x[4 * i + 1] += b.y; x[4 * i + 2] += b.z; x[4 * i + 3] += b.w;
-                }
-            } else {
-                const uint4* bp = reinterpret_cast<const uint4*>(e.bias + static_cast<size_t>(col) * 2);
-                float b[8];
-                unpack8_bf16(__ldg(bp), b);
-#pragma unroll
-                for (int i = 0; i < 8; i++) x[i] += b[i];
-                unpack8_bf16(__ldg(bp + 1), b);
-#pragma unroll
-                for (int i = 0; i < 8; i++) x[8 + i] += b[i];
-            }
+        for (int i = 0; i < 4; i++) {
+            const float4 b = *reinterpret_cast<const float4*>(bias16 + 4 * i);
+            x[4 * i + 0] = fmaf(v[16 * H + 4 * i + 0], e.scale, b.x);
+            x[4 * i + 1] = fmaf(v[16 * H + 4 * i + 1], e.scale, b.y);
+            x[4 * i + 2] = fmaf(v[16 * H + 4 * i + 2], e.scale, b.z);
+            x[4 * i + 3] = fmaf(v[16 * H + 4 * i + 3], e.scale, b.w);
         }
         if constexpr (OP == OP_FC1) {
+            if (!(e.flags & DBG_SKIP_GELU)) {
 #pragma unroll
-            for (int i = 0; i < 16; i++) x[i] = gelu_tanh_fast(x[i]);
-        } else {  // OP_FC2: (acc + bias) + residual, fc2.cu:27-46
-            if (e.side_row != nullptr) {
-                float r[8];
-                unpack8_bf16(__ldg(reinterpret_cast<const uint4*>(e.side_row + col)), r);
-#pragma unroll
-                for (int i = 0; i < 8; i++) x[i] += r[i];
-                unpack8_bf16(__ldg(reinterpret_cast<const uint4*>(e.side_row + col + 8)), r);
-#pragma unroll
-                for (int i = 0; i < 8; i++) x[8 + i] += r[i];
+                for (int i = 0; i < 16; i++) x[i] = gelu_tanh_fast(x[i]);
             }
+        } else {  // OP_FC2: (acc + bias) + residual, fc2.cu:27-46
+            float r[8];
+            unpack8_bf16(side_lo, r);
+#pragma unroll
+            for (int i = 0; i < 8; i++) x[i] += r[i];
+            unpack8_bf16(side_hi, r);
+#pragma unroll
+            for (int i = 0; i < 8; i++) x[8 + i] += r[i];
         }
         if constexpr (OUT == OUT_BF16) {
 #pragma unroll
@@ -254,6 +276,20 @@ __device__ __forceinline__ void epilogue_16(const float (&v)[32], const EpiRow& 
     }
 }
 
+// Bias values of columns col0 + lane + 32 i (i < NB) as fp32; zero past N or without a bias.
+template <int NB>
+__device__ __forceinline__ void load_bias(float (&b)[NB], const void* bias, unsigned flags, int col0, int lane, int N) {
+#pragma unroll
+    for (int i = 0; i < NB; i++) {
+        const int col = col0 + lane + 32 * i;
+        float val = 0.0f;
+        if (bias != nullptr && col < N)
+            val = (flags & FLAG_BIAS_F32) ? __ldg(static_cast<const float*>(bias) + col)
+                                          : __bfloat162float(__ldg(static_cast<const __nv_bfloat16*>(bias) + col));
+        b[i] = val;
+    }
+}
+
 template <int CG, int TN, int STAGES, int EPI_WARPS, int OP, int OUT, bool TMA_STORE>
 __global__ void __launch_bounds__((2 + EPI_WARPS) * 32, 1)
 sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -266,7 +302,8 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     uint8_t* const base_ptr = smem_raw + (base - raw_u32);
 
     const uint32_t staging_base = base + STAGES * T::STAGE_BYTES;
-    const uint32_t bar_base = staging_base + T::STAGING_BYTES;
+    const uint32_t bias_base = staging_base + T::STAGING_BYTES;
+    const uint32_t bar_base = bias_base + T::BIAS_BYTES;
     // barrier block: full[STAGES] | empty[STAGES] | tmem_full[2] | tmem_empty[2] | tmem ptr | abort
     const uint32_t full_bar0 = bar_base;
     const uint32_t empty_bar0 = bar_base + 8 * STAGES;
@@ -300,7 +337,7 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     if (warp == 1) {
         if (lane == 0) {
             for (int s = 0; s < STAGES; s++) {
-                mbar_init(full_bar0 + 8 * s, CG);   // one arrive.expect_tx per CTA of the pair
+                mbar_init(full_bar0 + 8 * s, 1);    // one arrive.expect_tx (the leader's, for the whole pair)
                 mbar_init(empty_bar0 + 8 * s, 1);   // one tcgen05.commit
             }
             for (int b = 0; b < 2; b++) {
@@ -330,6 +367,10 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            const bool prof = p.prof != nullptr;
+            const uint32_t full_bar_leader = (CG == 2) ? map_to_cta(full_bar0, 0) : full_bar0;
+            long long t_wait = 0;
+            const long long t_begin = clock64();
             for (int tile = cluster_id; ok && tile < p.num_tiles; tile += num_clusters) {
                 wc.tile = tile;
                 const int tm = tile / p.tiles_n;
@@ -337,13 +378,21 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const int m0 = tm * (T::TILE_M_CTA * CG) + static_cast<int>(cta_rank) * T::TILE_M_CTA;
                 const int nb = tn * TN + static_cast<int>(cta_rank) * T::B_ROWS;
                 for (int kb = 0; kb < p.k_blocks; kb++) {
+                    const long long t0 = prof ? clock64() : 0;
                     ok = wait_bar(empty_bar0 + 8 * stage, phase ^ 1u, wc, ST_PRODUCER_EMPTY_WAIT, stage);
+                    if (prof) t_wait += clock64() - t0;
                     if (!ok) break;
                     const uint32_t a_dst = base + stage * T::STAGE_BYTES;
                     const uint32_t b_dst = a_dst + T::A_BYTES;
-                    if constexpr (CG == 2) {
-                        const uint32_t bar = map_to_cta(full_bar0 + 8 * stage, 0);   // the leader's barrier
-                        mbar_arrive_expect_tx_cluster(bar, T::STAGE_BYTES);
+                    if (p.flags & DBG_SKIP_LOAD) {   // measurement aid: MMAs run on whatever shared memory holds
+                        if (cta_rank == 0) mbar_arrive(full_bar0 + 8 * stage);
+                    } else if constexpr (CG == 2) {
+                        // Both CTAs' copies complete on the LEADER's barrier.  Only the leader arrives on it,
+                        // announcing the bytes of the whole pair; the peer's copies just count down (the
+                        // transaction count may run negative until the leader's arrive lands, and the phase
+                        // cannot complete before that arrive).
+                        const uint32_t bar = full_bar_leader + 8 * stage;
+                        if (cta_rank == 0) mbar_arrive_expect_tx(full_bar0 + 8 * stage, 2 * T::STAGE_BYTES);
                         tma_load_2d_pair(a_dst, &map_a, kb * T::TILE_K, m0, bar);
                         tma_load_2d_pair(b_dst, &map_b, kb * T::TILE_K, nb, bar);
                     } else {
@@ -354,6 +403,11 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
+            }
+            if (prof) {
+                long long* slot = p.prof + static_cast<size_t>(blockIdx.x) * PROF_SLOTS;
+                slot[PROF_PRODUCER_WAIT] = t_wait;
+                slot[PROF_PRODUCER_TOTAL] = clock64() - t_begin;
             }
         }
         __syncwarp();
@@ -366,14 +420,21 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
+            const bool prof = p.prof != nullptr;
+            long long t_full = 0, t_tmem = 0, n_tiles = 0;
+            const long long t_begin = clock64();
             for (int tile = cluster_id; ok && tile < p.num_tiles; tile += num_clusters) {
                 wc.tile = tile;
+                long long t0 = prof ? clock64() : 0;
                 ok = wait_bar(tempty_bar0 + 8 * acc, acc_phase ^ 1u, wc, ST_MMA_TMEM_EMPTY_WAIT, acc);
+                if (prof) { t_tmem += clock64() - t0; n_tiles++; }
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * T::ACC_STRIDE;
                 for (int kb = 0; kb < p.k_blocks; kb++) {
+                    t0 = prof ? clock64() : 0;
                     ok = wait_bar(full_bar0 + 8 * stage, phase, wc, ST_MMA_FULL_WAIT, stage);
+                    if (prof) t_full += clock64() - t0;
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t a_src = base + stage * T::STAGE_BYTES;
@@ -395,6 +456,13 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 acc ^= 1;
                 if (acc == 0) acc_phase ^= 1u;
             }
+            if (prof) {
+                long long* slot = p.prof + static_cast<size_t>(blockIdx.x) * PROF_SLOTS;
+                slot[PROF_MMA_WAIT_FULL] = t_full;
+                slot[PROF_MMA_WAIT_TMEM] = t_tmem;
+                slot[PROF_MMA_TOTAL] = clock64() - t_begin;
+                slot[PROF_TILES] = n_tiles;
+            }
         }
         __syncwarp();
     } else {
@@ -407,16 +475,34 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         EpiRow e;
         e.scale = (p.scale_a ? __ldg(p.scale_a) : 1.0f) * (p.scale_b ? __ldg(p.scale_b) : 1.0f);
         e.inv_out = __frcp_rn(p.out_scale ? __ldg(p.out_scale) : 1.0f);   // IEEE 1/x, as the CPU oracle computes it
-        e.bias = static_cast<const uint8_t*>(p.bias);
         e.flags = p.flags;
         e.swz = lane & 7;
         e.stage_row = lane * 128;
-        const uint32_t my_staging = staging_base + ew * 2 * T::REGION_BYTES;
-        uint32_t region_seq = 0;                   // staging regions used so far: selects the double buffer
+        e.side_row = nullptr;
+        const uint32_t my_staging = staging_base + ew * T::STAGING_BUFS * T::REGION_BYTES;
+        uint32_t region_seq = 0;                   // staging regions used so far: selects the buffer
+
+        constexpr bool HAS_BIAS = (OP != OP_PE);
+        constexpr bool HAS_SIDE = (OP != OP_FC1);
+        constexpr int NB = T::COLS_PER_WARP / 32;  // bias values each lane stages per tile
+        float* const bias_w = reinterpret_cast<float*>(base_ptr + (bias_base - base)) + ew * T::COLS_PER_WARP;
+        float bnext[NB];
+        if constexpr (HAS_BIAS) {
+            if (cluster_id < p.num_tiles) {
+                const int tn0 = cluster_id % p.tiles_n;
+                load_bias<NB>(bnext, p.bias, p.flags, tn0 * TN + col_begin, lane, p.N);
+#pragma unroll
+                for (int i = 0; i < NB; i++) bias_w[lane + 32 * i] = bnext[i];
+                __syncwarp();
+            }
+        }
 
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
+        const bool prof = p.prof != nullptr && ew == 0;
+        long long t_acc = 0, t_store = 0, t_ld = 0;
+        const long long t_begin = clock64();
         for (int tile = cluster_id; tile < p.num_tiles; tile += num_clusters) {
             wc.tile = tile;
             const int tm = tile / p.tiles_n;
@@ -425,10 +511,25 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const long long row = m_warp + lane;
             const int n0 = tn * TN;
 
-            ok = wait_bar(tfull_bar0 + 8 * acc, acc_phase, wc, ST_EPI_TMEM_FULL_WAIT, acc);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tc_fence_after();
+            // Work for the NEXT tile that can overlap this one: its bias (registers now, shared memory
+            // once this tile is done) and, for FC2, an L2 prefetch of this lane's residual row segment.
+            const int next_tile = tile + num_clusters;
+            const bool has_next = next_tile < p.num_tiles;
+            if (has_next && (HAS_BIAS || OP == OP_FC2)) {
+                const int ntm = next_tile / p.tiles_n;
+                const int ntn = next_tile - ntm * p.tiles_n;
+                if constexpr (HAS_BIAS) load_bias<NB>(bnext, p.bias, p.flags, ntn * TN + col_begin, lane, p.N);
+                if constexpr (OP == OP_FC2) {
+                    const long long nrow = static_cast<long long>(ntm) * (T::TILE_M_CTA * CG) + cta_rank * T::TILE_M_CTA + quad * 32 + lane;
+                    if (nrow < p.M && !(p.flags & DBG_SKIP_SIDE)) {
+                        const __nv_bfloat16* r = p.side + nrow * p.ld_side + ntn * TN + col_begin;
+#pragma unroll
+                        for (int j = 0; j < T::COLS_PER_WARP / 64; j++)
+                            if (ntn * TN + col_begin + 64 * j < p.N)
+                                asm volatile("prefetch.global.L2 [%0];" ::"l"(r + 64 * j));
+                    }
+                }
+            }
 
             const bool row_ok = row < p.M;
             e.out_row = row_ok ? static_cast<uint8_t*>(p.D) + static_cast<size_t>(row) * p.ldd * T::OUT_BYTES : nullptr;
@@ -436,8 +537,18 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 e.side_row = row_ok ? p.side + ((row + p.row_phase) % p.period) * p.ld_side : nullptr;
             else if constexpr (OP == OP_FC2)
                 e.side_row = row_ok ? p.side + row * p.ld_side : nullptr;
-            else
-                e.side_row = nullptr;
+            if (p.flags & DBG_SKIP_SIDE) e.side_row = nullptr;
+
+            // Side values of the first chunk are requested before the accumulator is waited for.
+            uint4 side_cur[4], side_nxt[4];
+            if constexpr (HAS_SIDE) load_side32(side_cur, e.side_row, n0 + col_begin, p.N);
+
+            long long t0 = prof ? clock64() : 0;
+            ok = wait_bar(tfull_bar0 + 8 * acc, acc_phase, wc, ST_EPI_TMEM_FULL_WAIT, acc);
+            ok = __all_sync(0xffffffffu, ok);
+            if (prof) t_acc += clock64() - t0;
+            if (!ok) break;
+            tc_fence_after();
 
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * T::ACC_STRIDE;
             const bool warp_rows_ok = m_warp < p.M;      // warp-uniform: any row of this warp inside M
@@ -445,32 +556,46 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll 1
             for (int c = col_begin; c < col_begin + T::COLS_PER_WARP; c += 32) {
                 const int col = n0 + c;
-                if (col >= p.N) break;                   // warp-uniform: rest of the tile is past N
+                if (col >= p.N || (p.flags & DBG_SKIP_EPILOGUE)) break;   // warp-uniform: rest of the tile is past N
                 float v[32];
                 tmem_ld_32x32(t_row + c, v);
+                // next chunk's side values travel while this chunk is computed
+                if constexpr (HAS_SIDE) {
+                    if (c + 32 < col_begin + T::COLS_PER_WARP) load_side32(side_nxt, e.side_row, col + 32, p.N);
+                }
 
                 uint32_t region_base = 0;
                 int chunk16 = 0;
                 if constexpr (TMA_STORE) {
                     const int in_region = (c - col_begin) % T::REGION_COLS;
                     if (in_region == 0) {
-                        // The buffer about to be written was handed to TMA two regions ago.
-                        if (lane == 0) tma_store_wait_read<1>();
+                        // The buffer about to be written must no longer be read by an earlier TMA store.
+                        t0 = prof ? clock64() : 0;
+                        if (lane == 0) tma_store_wait_read<T::STAGING_BUFS - 1>();
                         __syncwarp();
+                        if (prof) t_store += clock64() - t0;
                     }
-                    region_base = my_staging + (region_seq & 1u) * T::REGION_BYTES;
+                    region_base = my_staging + (region_seq % T::STAGING_BUFS) * T::REGION_BYTES;
                     chunk16 = in_region * T::OUT_BYTES / 16;
                 }
+                t0 = prof ? clock64() : 0;
                 tmem_ld_wait();
+                if (prof) t_ld += clock64() - t0;
 
-                epilogue_16<OP, OUT, TMA_STORE, 0>(v, e, col, region_base, chunk16);
+                const float* bias32 = bias_w + (c - col_begin);
+                epilogue_16<OP, OUT, TMA_STORE, 0>(v, e, bias32, side_cur[0], side_cur[1], col, region_base, chunk16);
                 if (col + 16 < p.N)
-                    epilogue_16<OP, OUT, TMA_STORE, 1>(v, e, col + 16, region_base, chunk16 + 16 * T::OUT_BYTES / 16);
+                    epilogue_16<OP, OUT, TMA_STORE, 1>(v, e, bias32 + 16, side_cur[2], side_cur[3], col + 16, region_base,
+                                                       chunk16 + T::OUT_BYTES);
+                if constexpr (HAS_SIDE) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) side_cur[i] = side_nxt[i];
+                }
 
                 if constexpr (TMA_STORE) {
                     const int in_region = (c - col_begin) % T::REGION_COLS;
                     const bool region_done = (in_region + 32 == T::REGION_COLS) || (col + 32 >= p.N);
-                    if (region_done) {
+                    if (region_done && !(p.flags & DBG_SKIP_STORE)) {
                         fence_proxy_async_smem();
                         __syncwarp();
                         if (lane == 0 && warp_rows_ok) {
@@ -491,10 +616,25 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             }
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1u;
+
+            if constexpr (HAS_BIAS) {
+                if (has_next) {   // every lane has finished reading this tile's bias (the __syncwarp above)
+#pragma unroll
+                    for (int i = 0; i < NB; i++) bias_w[lane + 32 * i] = bnext[i];
+                    __syncwarp();
+                }
+            }
         }
         if constexpr (TMA_STORE) {
             if (lane == 0) tma_store_wait_all<0>();
             __syncwarp();
+        }
+        if (prof && lane == 0) {
+            long long* slot = p.prof + static_cast<size_t>(blockIdx.x) * PROF_SLOTS;
+            slot[PROF_EPI_WAIT_ACC] = t_acc;
+            slot[PROF_EPI_WAIT_STORE] = t_store;
+            slot[PROF_EPI_WAIT_LD] = t_ld;
+            slot[PROF_EPI_TOTAL] = clock64() - t_begin;
         }
     }
 

@@ -87,8 +87,11 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
+// Arrival on a barrier of any CTA of the cluster.  CTA-scope release is enough for its one use
+// (handing a TMEM accumulator back): the tensor-memory reads are ordered before it by
+// tcgen05.fence::before_thread_sync, and no shared-memory data is published through it.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+    asm volatile("mbarrier.arrive.release.cta.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
 // ---------------------------------------------------------------- cluster barrier

@@ -16,18 +16,19 @@
 //   TMA_STORE  1 = swizzled staging + TMA tensor stores, 0 = 16-byte stores from registers
 #define SL8_VARIANT_LIST(X) \
     X(0, 1, 256, 4, 4, 0)   \
-    X(1, 1, 256, 4, 4, 1)   \
+    X(1, 1, 256, 3, 4, 1)   \
     X(2, 2, 256, 6, 4, 0)   \
-    X(3, 2, 256, 6, 4, 1)   \
+    X(3, 2, 256, 5, 4, 1)   \
     X(4, 2, 256, 5, 8, 1)   \
     X(5, 2, 256, 6, 8, 0)   \
     X(6, 2, 192, 6, 4, 1)   \
     X(7, 2, 192, 7, 4, 0)   \
-    X(8, 1, 128, 6, 4, 1)   \
-    X(9, 2, 128, 8, 4, 1)   \
-    X(10, 1, 256, 4, 8, 0)
+    X(8, 1, 128, 5, 4, 1)   \
+    X(9, 2, 128, 7, 4, 1)   \
+    X(10, 1, 256, 4, 8, 0)  \
+    X(11, 2, 256, 4, 8, 1)
 
-#define SL8_NUM_VARIANTS 11
+#define SL8_NUM_VARIANTS 12
 
 namespace sl8 {
 

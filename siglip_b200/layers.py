@@ -176,6 +176,22 @@ class Engine:
         self._check(self._lib.sl8_device_status(self._h, self._stream(stream), C.byref(detail)))
 
 
+    # ------------------------------------------------------------------ tracing
+    TRACE_FIELDS = ("producer_wait", "producer_total", "mma_wait_operands", "mma_wait_accumulator", "mma_total",
+                    "epi_wait_accumulator", "epi_total", "epi_wait_store", "tiles", "epi_wait_tmem_load")
+
+    def trace_enable(self, on: bool = True) -> None:
+        self._check(self._lib.sl8_trace_enable(self._h, 1 if on else 0))
+
+    def trace_read(self, max_blocks: int = 512) -> list:
+        """Per-CTA cycle totals of the last launch (see sl8_trace_read)."""
+        buf = (C.c_longlong * (max_blocks * 16))()
+        n = self._lib.sl8_trace_read(self._h, buf, max_blocks)
+        if n < 0:
+            self._check(n)
+        return [{k: buf[b * 16 + i] for i, k in enumerate(self.TRACE_FIELDS)} for b in range(n)]
+
+
 def num_variants() -> int:
     return _l.load_library().sl8_num_variants()
 

@@ -110,7 +110,7 @@ def test_patch_embed_period_wrap(engine, oracle):
     run_pe(engine, oracle, 3 * 729 + 5, 1152, 588, period=729, seed=8)
 
 
-@pytest.mark.parametrize("vid", range(11))
+@pytest.mark.parametrize("vid", range(12))
 def test_every_variant(engine, oracle, vid):
     assert vid < num_variants()
     engine.set_variant(vid)
