@@ -91,7 +91,7 @@ typedef struct sl8_config {
     int tile_k;        /* K bytes per pipeline stage                                         */
     int stages;        /* depth of the TMA -> MMA shared-memory ring                          */
     int epi_warps;     /* epilogue warps per CTA                                              */
-    int tma_store;     /* 1 = swizzled shared staging + TMA tensor store, 0 = direct stores  */
+    int staging_buffers; /* swizzled staging regions per epilogue warp (1 = FC1 only)          */
     int grid;          /* CTAs launched                                                      */
     int smem_bytes;    /* dynamic shared memory per CTA                                      */
     int variant_id;    /* index usable with SL8_FORCE_VARIANT / sl8_set_variant              */
@@ -217,6 +217,10 @@ int sl8_set_wait_budget_ms(sl8_handle_t h, int ms);
  *   [4] MMA thread total                        [5] epilogue warp 0 waiting for an accumulator
  *   [6] epilogue warp 0 total                   [7] epilogue warp 0 waiting for staging to drain
  *   [8] tiles of this CTA pair                  [9] epilogue warp 0 waiting for tcgen05.ld
+ *   [10] epilogue warp 0 transform + staging    [11] epilogue warp 0 proxy fence + store issue
+ *   [12] epilogue warp 0 waiting until the previous store has read its staging buffer
+ *   [13] epilogue warp 0 issuing the side-data prefetch
+ *   [14] MMA thread issuing tcgen05.mma         [15] MMA thread issuing tcgen05.commit
  * sl8_trace_read synchronises the device and copies min(grid of the last launch, max_blocks)
  * records into out[max_blocks * SL8_TRACE_SLOTS]; returns the number of records or an error. */
 #define SL8_TRACE_SLOTS 16

@@ -27,6 +27,8 @@ LIB = PKG / "lib" / "libsiglip_fp8.so"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH_FLAGS + ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hidden",
                            "-Xptxas", "-v"]
+if os.environ.get("SL8_DIAG"):          # measurement aids in the kernels (see SL8_DBG in sl8_kernel.cuh)
+    NVCC_FLAGS.append("-DSL8_DIAG")
 
 
 def nvcc() -> str:
@@ -68,6 +70,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if LIB.exists() and not force and LIB.stat().st_mtime >= sources_mtime():
         return LIB
     OBJ.mkdir(parents=True, exist_ok=True)
+    for stale in list(OBJ.glob("variant_*.o")) + list(OBJ.glob("variant_*.log")):
+        stale.unlink()
     exe = nvcc()
     jobs = []
     objs = []

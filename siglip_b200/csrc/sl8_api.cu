@@ -30,7 +30,7 @@ typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_
 
 const VariantEntry* variant(int id) {
     switch (id) {
-#define SL8_CASE(id_, CG, TN, ST, EW, TS) \
+#define SL8_CASE(id_, CG, TN, TK, ST, EW, NB) \
     case id_:                             \
         return sl8_variant_##id_();
         SL8_VARIANT_LIST(SL8_CASE)
@@ -70,6 +70,7 @@ struct sl8_context {
     int last_grid = 0;
     encode_tiled_fn encode = nullptr;
     int forced_variant = -1;
+    int max_clusters_override = 0;      // SL8_MAX_CLUSTERS: measurement aid, caps the persistent grid
     unsigned wait_budget_ms = 2000;
     bool smem_attr_set[SL8_NUM_VARIANTS][sl8::K_COUNT] = {};
     int max_clusters[SL8_NUM_VARIANTS][sl8::K_COUNT] = {};
@@ -114,14 +115,13 @@ int pick_variant(int op, int out_dtype, long long M, int N, int K) {
     const long long tiles256 = ((M + 255) / 256) * ((N + 255) / 256);
     if (tiles256 < 74) {
         // Too few 256 x 256 tiles to fill the GPU: smaller tiles give more of the 148 SMs work.
-        return (M <= 128) ? 8 : 9;
+        return (M <= 128) ? 6 : 7;
     }
     // A tcgen05.mma of a CTA pair takes about 150 cycles whatever its N (measured for N = 128, 192,
     // 256), so the widest tile does the most work per instruction even where N = 1152 leaves the
     // fifth 256-wide tile half empty.
-    if (op == SL8_OP_FC1_GELU) return 4;   // GELU epilogue: two epilogue warps per scheduler
-    if (op == SL8_OP_PATCH_EMBED) return 4;
-    return 3;
+    if (op == SL8_OP_FC1_GELU) return 2;   // GELU epilogue: two epilogue warps per scheduler
+    return 1;
 }
 
 struct Problem {
@@ -148,7 +148,7 @@ int validate(sl8_handle_t h, const Problem& q) {
     if (q.M > 0x7FFFFF00ll) return fail(h, SL8_ERR_UNSUPPORTED, "M exceeds 2^31 rows");
     if (q.out_dtype != SL8_OUT_BF16 && q.out_dtype != SL8_OUT_E4M3)
         return fail(h, SL8_ERR_INVALID_VALUE, "unknown out_dtype");
-    if (q.flags & ~(unsigned)(SL8_FLAG_BIAS_F32 | SL8_FLAG_PE_F32_ADD | 0xFF00u)) return fail(h, SL8_ERR_INVALID_VALUE, "unknown flag bits");
+    if (q.flags & ~(unsigned)(SL8_FLAG_BIAS_F32 | SL8_FLAG_PE_F32_ADD | 0x1FF00u)) return fail(h, SL8_ERR_INVALID_VALUE, "unknown flag bits");
     if (q.N % 16 != 0) return fail(h, SL8_ERR_UNSUPPORTED, "N must be a multiple of 16");
     if (q.lda < q.K || q.ldb < q.K) return fail(h, SL8_ERR_INVALID_VALUE, "lda / ldb smaller than K");
     if (q.ldd < q.N) return fail(h, SL8_ERR_INVALID_VALUE, "ldd smaller than N");
@@ -221,7 +221,8 @@ int grid_for(sl8_handle_t h, const VariantEntry* v, int slot, int num_tiles) {
         }
         cached = clusters > 0 ? clusters : 1;
     }
-    const int clusters = num_tiles < cached ? num_tiles : cached;
+    int clusters = num_tiles < cached ? num_tiles : cached;
+    if (h->max_clusters_override > 0 && clusters > h->max_clusters_override) clusters = h->max_clusters_override;
     return clusters * v->cg;
 }
 
@@ -237,6 +238,7 @@ int run(sl8_handle_t h, const Problem& q, cudaStream_t stream) {
     if (!v) return fail(h, SL8_ERR_INVALID_VALUE, "no such kernel variant");
     const int slot = kernel_slot(q.op, q.out_dtype);
     const int ob = (q.out_dtype == SL8_OUT_BF16) ? 2 : 1;
+    if (!v->kernel[slot]) return fail(h, SL8_ERR_UNSUPPORTED, "the forced kernel variant has one staging buffer and serves FC1 only");
 
     if (!h->smem_attr_set[vid][slot]) {
         cudaError_t e = cudaFuncSetAttribute(v->kernel[slot], cudaFuncAttributeMaxDynamicSharedMemorySize, v->smem_bytes[slot]);
@@ -251,13 +253,21 @@ int run(sl8_handle_t h, const Problem& q, cudaStream_t stream) {
     rc = encode_2d(h, &map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q.B, (unsigned long long)q.K, (unsigned long long)q.N,
                    (unsigned long long)q.ldb, 128, (unsigned)(v->tn / v->cg), CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
     if (rc != SL8_OK) return rc;
-    if (v->tma_store_slot[slot]) {
-        rc = encode_2d(h, &map_d, ob == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, ob, q.D,
-                       (unsigned long long)q.N, (unsigned long long)q.M, (unsigned long long)q.ldd * ob,
-                       (unsigned)(128 / ob), 32, CU_TENSOR_MAP_L2_PROMOTION_NONE);
+    rc = encode_2d(h, &map_d, ob == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, ob, q.D,
+                   (unsigned long long)q.N, (unsigned long long)q.M, (unsigned long long)q.ldd * ob,
+                   (unsigned)(128 / ob), 32, CU_TENSOR_MAP_L2_PROMOTION_NONE);
+    if (rc != SL8_OK) return rc;
+
+    // Side data (table [period, N] or residual [M, N], bf16) comes in by TMA as 32-row x 64-column boxes.
+    CUtensorMap map_s = map_d;
+    if (q.op == SL8_OP_PATCH_EMBED) {
+        rc = encode_2d(h, &map_s, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, q.side, (unsigned long long)q.N,
+                       (unsigned long long)q.period, (unsigned long long)q.ld_side * 2, 64, 32, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
         if (rc != SL8_OK) return rc;
-    } else {
-        map_d = map_a;   // unused by the kernel; any valid map
+    } else if (q.op == SL8_OP_FC2_RESIDUAL) {
+        rc = encode_2d(h, &map_s, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, q.side, (unsigned long long)q.N,
+                       (unsigned long long)q.M, (unsigned long long)q.ld_side * 2, 64, 32, CU_TENSOR_MAP_L2_PROMOTION_NONE);
+        if (rc != SL8_OK) return rc;
     }
 
     KernelParams p;
@@ -271,8 +281,8 @@ int run(sl8_handle_t h, const Problem& q, cudaStream_t stream) {
     const long long nt = tiles_m * p.tiles_n;
     if (nt > 0x7FFFFFFFll) return fail(h, SL8_ERR_UNSUPPORTED, "too many tiles");
     p.num_tiles = static_cast<int>(nt);
-    p.k_blocks = (q.K + 127) / 128;
-    const int k_last = q.K - (p.k_blocks - 1) * 128;
+    p.k_blocks = (q.K + v->tk - 1) / v->tk;
+    const int k_last = q.K - (p.k_blocks - 1) * v->tk;
     p.last_kblock_mmas = (k_last + 31) / 32;
     p.scale_a = q.scale_a;
     p.scale_b = q.scale_b;
@@ -292,7 +302,7 @@ int run(sl8_handle_t h, const Problem& q, cudaStream_t stream) {
     const int grid = grid_for(h, v, slot, p.num_tiles);
     h->last_grid = grid;
     if (h->d_prof && grid > h->prof_blocks) return fail(h, SL8_ERR_INVALID_VALUE, "tracing buffer smaller than the grid");
-    cudaError_t e = v->launch[slot](&map_a, &map_b, &map_d, &p, grid, stream);
+    cudaError_t e = v->launch[slot](&map_a, &map_b, &map_d, &map_s, &p, grid, stream);
     if (e != cudaSuccess) return fail_cuda(h, e, "kernel launch");
     return SL8_OK;
 }
@@ -301,10 +311,10 @@ void fill_config(const VariantEntry* v, int slot, int grid, sl8_config* out) {
     out->cta_group = v->cg;
     out->tile_m = 128 * v->cg;
     out->tile_n = v->tn;
-    out->tile_k = 128;
+    out->tile_k = v->tk;
     out->stages = v->stages;
     out->epi_warps = v->epi_warps;
-    out->tma_store = v->tma_store_slot[slot];
+    out->staging_buffers = v->nbuf;
     out->grid = grid;
     out->smem_bytes = v->smem_bytes[slot];
     out->variant_id = v->id;
@@ -362,6 +372,8 @@ SL8_API int sl8_create(sl8_handle_t* out, int device) {
         delete h;
         return fail_cuda(nullptr, e, "cudaMemset(status block)");
     }
+    const char* mc = getenv("SL8_MAX_CLUSTERS");
+    if (mc && *mc) h->max_clusters_override = atoi(mc);
     const char* fv = getenv("SL8_FORCE_VARIANT");
     if (fv && *fv) {
         const int id = atoi(fv);
@@ -634,8 +646,9 @@ SL8_API int sl8_device_status(sl8_handle_t h, sl8_stream_t stream, unsigned deta
     cudaMemset(h->d_status, 0, 16);
     char buf[160];
     static const char* names[] = {"", "producer waiting for a free stage", "MMA thread waiting for operands",
-                                  "MMA thread waiting for a free accumulator", "epilogue waiting for an accumulator"};
-    snprintf(buf, sizeof buf, "device wait expired: %s (index %u, tile %u, block %u)", st[0] < 5 ? names[st[0]] : "?", st[1],
+                                  "MMA thread waiting for a free accumulator", "epilogue waiting for an accumulator",
+                                  "epilogue waiting for table / residual data"};
+    snprintf(buf, sizeof buf, "device wait expired: %s (index %u, tile %u, block %u)", st[0] < 6 ? names[st[0]] : "?", st[1],
              st[2], st[3]);
     return fail(h, SL8_ERR_DEVICE_TIMEOUT, buf);
 }

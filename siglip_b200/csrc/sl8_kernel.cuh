@@ -15,8 +15,9 @@
 //   warps 2..     epilogue: tcgen05.ld of the finished accumulator (two accumulators in TMEM,
 //                 so the MMA of tile i+1 overlaps the epilogue of tile i), dequantisation
 //                 scale, fused bias / GELU / residual / table add, conversion to bf16 or
-//                 e4m3, and either direct 16-byte global stores or swizzled shared staging
-//                 followed by TMA tensor stores.
+//                 e4m3 into swizzled shared staging, TMA tensor stores.  The residual / table
+//                 values of a 32-row x 128-byte region are brought into that same staging buffer
+//                 by a TMA load a few regions ahead, added in place and stored from there.
 //
 // CG == 2 runs a CTA pair per tile (cluster of two, tcgen05 cta_group::2): each CTA loads its
 // own 128 rows of A and half of the tile's B rows, the leader issues 256 x TN MMAs that read
@@ -36,9 +37,18 @@ namespace sl8 {
 
 enum : int { OP_PE = 0, OP_FC1 = 1, OP_FC2 = 2 };
 enum : int { OUT_BF16 = 0, OUT_E4M3 = 1 };
+// Measurement aids (skip one part of the kernel to time the rest).  They cost instructions in the
+// hot loops, so they exist only in a library built with -DSL8_DIAG.
+#ifdef SL8_DIAG
+#define SL8_DBG(flags, bit) (((flags) & (bit)) != 0u)
+#else
+#define SL8_DBG(flags, bit) false
+#endif
+
 enum : unsigned { FLAG_BIAS_F32 = 1u, FLAG_PE_F32_ADD = 2u,
                   DBG_SKIP_SIDE = 0x100u, DBG_SKIP_GELU = 0x200u, DBG_SKIP_BIAS = 0x400u, DBG_SKIP_STORE = 0x800u,
-                  DBG_SKIP_LOAD = 0x1000u, DBG_SKIP_EPILOGUE = 0x2000u };
+                  DBG_SKIP_LOAD = 0x1000u, DBG_SKIP_EPILOGUE = 0x2000u, DBG_SKIP_MMA = 0x4000u,
+                  DBG_SKIP_A = 0x8000u, DBG_SKIP_B = 0x10000u };
 
 // status[0] codes: which role gave up.
 enum : uint32_t {
@@ -46,7 +56,8 @@ enum : uint32_t {
     ST_PRODUCER_EMPTY_WAIT = 1,
     ST_MMA_FULL_WAIT = 2,
     ST_MMA_TMEM_EMPTY_WAIT = 3,
-    ST_EPI_TMEM_FULL_WAIT = 4
+    ST_EPI_TMEM_FULL_WAIT = 4,
+    ST_EPI_SIDE_WAIT = 5
 };
 
 // Tracing slots written per CTA when KernelParams::prof is set (cycles, clock64).
@@ -61,6 +72,12 @@ enum : int {
     PROF_EPI_WAIT_STORE = 7,  // epilogue warp 0 waiting for staging to drain
     PROF_TILES = 8,
     PROF_EPI_WAIT_LD = 9,     // epilogue warp 0 waiting for tcgen05.ld
+    PROF_EPI_MATH = 10,       // epilogue warp 0: transform + staging writes
+    PROF_EPI_STORE_ISSUE = 11,// epilogue warp 0: proxy fence + TMA store issue
+    PROF_EPI_REFILL = 12,     // epilogue warp 0: waiting until the previous store has read its staging buffer
+    PROF_EPI_PREFETCH = 13,   // epilogue warp 0: issuing the side-data prefetch
+    PROF_MMA_ISSUE = 14,      // MMA thread: issuing tcgen05.mma
+    PROF_MMA_COMMIT = 15,     // MMA thread: issuing tcgen05.commit
     PROF_SLOTS = 16
 };
 
@@ -70,8 +87,8 @@ struct KernelParams {
     int K;
     int tiles_n;
     int num_tiles;
-    int k_blocks;          // ceil(K / 128)
-    int last_kblock_mmas;  // K = 32 steps needed in the last k-block (1..4)
+    int k_blocks;          // ceil(K / TILE_K)
+    int last_kblock_mmas;  // K = 32 steps needed in the last k-block (1 .. TILE_K / 32)
     const float* scale_a;
     const float* scale_b;
     const float* out_scale;
@@ -88,33 +105,37 @@ struct KernelParams {
     long long* prof;                 // optional: PROF_SLOTS clock64 totals per CTA (null = tracing off)
 };
 
-template <int CG, int TN, int STAGES, int EPI_WARPS, int OUT, bool TMA_STORE>
+template <int CG, int TN, int TK, int STAGES, int EPI_WARPS, int OUT, int NBUF>
 struct KernelTraits {
     static_assert(CG == 1 || CG == 2, "one CTA or a CTA pair per tile");
-    static_assert(TN == 128 || TN == 192 || TN == 256, "tile N");
+    static_assert(TN == 128 || TN == 256, "tile N");
     static_assert(EPI_WARPS == 4 || EPI_WARPS == 8, "one or two warps per TMEM lane quadrant");
+    static_assert(NBUF >= 1 && NBUF <= 4, "staging buffers per epilogue warp");
     static constexpr int TILE_M_CTA = 128;                       // rows per CTA = TMEM lanes
-    static constexpr int TILE_K = 128;                           // bytes of K per stage = swizzle span
+    static_assert(TK == 128 || TK == 256, "bytes of K per stage: one or two 128-byte swizzle atoms");
+    static constexpr int TILE_K = TK;                            // bytes of K per stage
+    static constexpr int KATOMS = TK / 128;                      // 128-byte swizzle atoms per stage and operand
     static constexpr int B_ROWS = TN / CG;                       // B rows this CTA loads per stage
-    static constexpr int A_BYTES = TILE_M_CTA * TILE_K;          // 16 KiB
-    static constexpr int B_BYTES = B_ROWS * TILE_K;
+    static constexpr int A_ATOM_BYTES = TILE_M_CTA * 128;        // 16 KiB: 128 rows x 128 bytes
+    static constexpr int B_ATOM_BYTES = B_ROWS * 128;
+    static constexpr int A_BYTES = KATOMS * A_ATOM_BYTES;
+    static constexpr int B_BYTES = KATOMS * B_ATOM_BYTES;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;        // also the bytes one CTA's TMA adds per stage
-    static constexpr int ACC_STRIDE = (TN <= 128) ? 128 : 256;   // TMEM columns between the two accumulators
-    static constexpr int TMEM_COLS = 2 * ACC_STRIDE;             // 256 or 512: a power of two >= 32
+    static constexpr int ACC_STRIDE = TN;                        // TMEM columns between the two accumulators
+    static constexpr int TMEM_COLS = 2 * TN;                     // 256 or 512: a power of two >= 32
     static constexpr int OUT_BYTES = (OUT == OUT_BF16) ? 2 : 1;
     static constexpr int REGION_COLS = 128 / OUT_BYTES;          // output columns in one 128-byte staging row
     static constexpr int REGION_BYTES = 32 * 128;                // 32 rows of one warp
-    // Staging buffers per epilogue warp: two (write one while TMA reads the other) with one warp
-    // per scheduler; one where a second warp on the same scheduler covers the wait instead.
-    static constexpr int STAGING_BUFS = (EPI_WARPS == 8) ? 1 : 2;
-    static constexpr int STAGING_BYTES = TMA_STORE ? EPI_WARPS * STAGING_BUFS * REGION_BYTES : 0;
+    static constexpr int STAGING_BYTES = EPI_WARPS * NBUF * REGION_BYTES;
     static constexpr int COLS_PER_WARP = TN / (EPI_WARPS / 4);   // columns one epilogue warp covers
+    static constexpr int REGIONS_PER_TILE = COLS_PER_WARP / REGION_COLS;
+    static constexpr int CHUNKS_PER_REGION = REGION_COLS / 32;   // 32-column tcgen05.ld chunks per region
     static constexpr int BIAS_BYTES = EPI_WARPS * COLS_PER_WARP * 4;   // fp32 bias of the current tile, one copy per warp
     static constexpr int THREADS = (2 + EPI_WARPS) * 32;
-    static constexpr int BAR_BYTES = 256;
+    static constexpr int BAR_BYTES = 512;                        // pipeline barriers + one per staging buffer
     static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STAGING_BYTES + BIAS_BYTES + BAR_BYTES;
     static_assert(STAGE_BYTES % 1024 == 0, "every operand tile must start on a swizzle-atom boundary");
-    static_assert(COLS_PER_WARP % REGION_COLS == 0 || !TMA_STORE, "a warp stores whole staging regions");
+    static_assert(COLS_PER_WARP % REGION_COLS == 0, "a warp stores whole staging regions");
     static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB a CTA may use");
 };
 
@@ -170,47 +191,41 @@ __device__ __forceinline__ void unpack8_bf16(const uint4& q, float (&f)[8]) {
     f[6] = bf16_lo_f32(q.w); f[7] = bf16_hi_f32(q.w);
 }
 
-// Everything an epilogue warp needs that does not change inside a tile.
-struct EpiRow {
-    float scale;                   // scale_a * scale_b
-    float inv_out;                 // 1 / out_scale
-    const __nv_bfloat16* side_row; // this lane's table / residual row, or null when the row is past M
-    uint8_t* out_row;              // this lane's output row (direct stores), or null when past M
-    uint32_t stage_row;            // byte offset of this lane's 128-byte staging row (TMA stores)
-    uint32_t swz;                  // (lane & 7): XOR applied to the 16-byte chunk index
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 r;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(addr));
+    return r;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+// Per-warp epilogue constants.
+struct EpiCtx {
+    float scale;      // scale_a * scale_b
+    float inv_out;    // 1 / out_scale
+    uint32_t row_off; // lane * 128: byte offset of this lane's row inside a staging region
+    uint32_t swz;     // lane & 7: XOR applied to the 16-byte piece index (SWIZZLE_128B)
     unsigned flags;
 };
 
-// 32 bf16 side values (table or residual) of one 32-column chunk of this lane's row; columns at
-// or past N are not read.
-__device__ __forceinline__ void load_side32(uint4 (&s)[4], const __nv_bfloat16* side_row, int col, int N) {
-#pragma unroll
-    for (int h = 0; h < 2; h++) {
-        if (side_row != nullptr && col + 16 * h < N) {
-            s[2 * h + 0] = __ldg(reinterpret_cast<const uint4*>(side_row + col + 16 * h));
-            s[2 * h + 1] = __ldg(reinterpret_cast<const uint4*>(side_row + col + 16 * h + 8));
-        } else {
-            s[2 * h + 0] = make_uint4(0, 0, 0, 0);
-            s[2 * h + 1] = make_uint4(0, 0, 0, 0);
-        }
-    }
-}
-
-// Transforms 16 accumulator columns (v[16*H .. 16*H+15] = columns col .. col+15 of this lane's row)
-// and stores them.  bias16 points at the 16 fp32 bias values of these columns in shared memory
-// (FC1 / FC2); side holds their 16 bf16 table / residual values (patch-embed / FC2).  `chunk16`
-// is the index of the first 16-byte piece inside the staging row when TMA stores are used.
-template <int OP, int OUT, bool TMA_STORE, int H>
-__device__ __forceinline__ void epilogue_16(const float (&v)[32], const EpiRow& e, const float* bias16,
-                                            const uint4& side_lo, const uint4& side_hi, int col, uint32_t region_base,
-                                            int chunk16) {
+// Transforms 16 accumulator columns (v[16*H .. 16*H+15]) of this lane's row and writes them to the
+// staging region at `region` (shared address), 16-byte pieces `piece0`.. of the lane's 128-byte row.
+// bias16: the 16 fp32 bias values of these columns in shared memory (FC1 / FC2).  With side data
+// (patch-embed table, FC2 residual) the 16 bf16 side values already sit in the staging region at the
+// very place the result goes; they are read, combined and overwritten.
+template <int OP, int OUT, int H>
+__device__ __forceinline__ void epilogue_16(const float (&v)[32], const EpiCtx& e, const float* bias16, uint32_t region,
+                                            int piece0) {
     float x[16];
     uint32_t w[8];  // bf16: 8 words (16 values); e4m3: 4 words used
+    const uint32_t a0 = region + e.row_off + (((piece0 + 0) ^ e.swz) << 4);
+    const uint32_t a1 = region + e.row_off + (((piece0 + 1) ^ e.swz) << 4);
 
     if constexpr (OP == OP_PE) {
+        const uint4 s0 = lds128(a0), s1 = lds128(a1);
 #pragma unroll
         for (int i = 0; i < 16; i++) x[i] = v[16 * H + i] * e.scale;
-        const uint32_t tw[8] = {side_lo.x, side_lo.y, side_lo.z, side_lo.w, side_hi.x, side_hi.y, side_hi.z, side_hi.w};
+        const uint32_t tw[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
         if (e.flags & FLAG_PE_F32_ADD) {
 #pragma unroll
             for (int i = 0; i < 8; i++)
@@ -232,16 +247,16 @@ __device__ __forceinline__ void epilogue_16(const float (&v)[32], const EpiRow& 
             x[4 * i + 3] = fmaf(v[16 * H + 4 * i + 3], e.scale, b.w);
         }
         if constexpr (OP == OP_FC1) {
-            if (!(e.flags & DBG_SKIP_GELU)) {
+            if (!SL8_DBG(e.flags, DBG_SKIP_GELU)) {
 #pragma unroll
                 for (int i = 0; i < 16; i++) x[i] = gelu_tanh_fast(x[i]);
             }
         } else {  // OP_FC2: (acc + bias) + residual, fc2.cu:27-46
             float r[8];
-            unpack8_bf16(side_lo, r);
+            unpack8_bf16(lds128(a0), r);
 #pragma unroll
             for (int i = 0; i < 8; i++) x[i] += r[i];
-            unpack8_bf16(side_hi, r);
+            unpack8_bf16(lds128(a1), r);
 #pragma unroll
             for (int i = 0; i < 8; i++) x[8 + i] += r[i];
         }
@@ -257,23 +272,8 @@ __device__ __forceinline__ void epilogue_16(const float (&v)[32], const EpiRow& 
             }
         }
     }
-
-    constexpr int PIECES = (OUT == OUT_BF16) ? 2 : 1;  // 16-byte pieces for 16 columns
-    if constexpr (TMA_STORE) {
-#pragma unroll
-        for (int p = 0; p < PIECES; p++) {
-            const uint32_t addr = region_base + e.stage_row + (((chunk16 + p) ^ e.swz) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * p + 0]), "r"(w[4 * p + 1]),
-                         "r"(w[4 * p + 2]), "r"(w[4 * p + 3])
-                         : "memory");
-        }
-    } else {
-        if (e.out_row != nullptr) {
-            uint4* dst = reinterpret_cast<uint4*>(e.out_row + static_cast<size_t>(col) * ((OUT == OUT_BF16) ? 2 : 1));
-#pragma unroll
-            for (int p = 0; p < PIECES; p++) dst[p] = make_uint4(w[4 * p + 0], w[4 * p + 1], w[4 * p + 2], w[4 * p + 3]);
-        }
-    }
+    sts128(a0, w[0], w[1], w[2], w[3]);
+    if constexpr (OUT == OUT_BF16) sts128(a1, w[4], w[5], w[6], w[7]);
 }
 
 // Bias values of columns col0 + lane + 32 i (i < NB) as fp32; zero past N or without a bias.
@@ -290,11 +290,12 @@ __device__ __forceinline__ void load_bias(float (&b)[NB], const void* bias, unsi
     }
 }
 
-template <int CG, int TN, int STAGES, int EPI_WARPS, int OP, int OUT, bool TMA_STORE>
+template <int CG, int TN, int TK, int STAGES, int EPI_WARPS, int OP, int OUT, int NBUF>
 __global__ void __launch_bounds__((2 + EPI_WARPS) * 32, 1)
 sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                const __grid_constant__ CUtensorMap map_d, const KernelParams p) {
-    using T = KernelTraits<CG, TN, STAGES, EPI_WARPS, OUT, TMA_STORE>;
+                const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_s,
+                const KernelParams p) {
+    using T = KernelTraits<CG, TN, TK, STAGES, EPI_WARPS, OUT, NBUF>;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_u32 = smem_u32(smem_raw);
@@ -313,7 +314,8 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     uint8_t* const bar_ptr = base_ptr + (bar_base - base);
     volatile uint32_t* const tmem_ptr = reinterpret_cast<volatile uint32_t*>(bar_ptr + 16 * STAGES + 32);
     volatile uint32_t* const abort_flag = tmem_ptr + 1;
-    static_assert(16 * STAGES + 32 + 8 <= T::BAR_BYTES, "barrier block too small");
+    const uint32_t side_bar0 = bar_base + 16 * STAGES + 48;     // EPI_WARPS * NBUF barriers: side data landed
+    static_assert(16 * STAGES + 48 + 8 * EPI_WARPS * NBUF <= T::BAR_BYTES, "barrier block too small");
 
     const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
     const int lane = threadIdx.x & 31;
@@ -332,7 +334,8 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         *abort_flag = 0u;
         prefetch_tensormap(&map_a);
         prefetch_tensormap(&map_b);
-        if constexpr (TMA_STORE) prefetch_tensormap(&map_d);
+        prefetch_tensormap(&map_d);
+        if constexpr (OP != OP_FC1) prefetch_tensormap(&map_s);
     }
     if (warp == 1) {
         if (lane == 0) {
@@ -344,6 +347,7 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 mbar_init(tfull_bar0 + 8 * b, 1);                  // one tcgen05.commit
                 mbar_init(tempty_bar0 + 8 * b, EPI_WARPS * CG);    // one arrival per epilogue warp of the pair
             }
+            for (int b = 0; b < EPI_WARPS * NBUF; b++) mbar_init(side_bar0 + 8 * b, 1);   // one arrive per fill
             fence_mbar_init();
         }
         __syncwarp();
@@ -384,7 +388,7 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     if (!ok) break;
                     const uint32_t a_dst = base + stage * T::STAGE_BYTES;
                     const uint32_t b_dst = a_dst + T::A_BYTES;
-                    if (p.flags & DBG_SKIP_LOAD) {   // measurement aid: MMAs run on whatever shared memory holds
+                    if (SL8_DBG(p.flags, DBG_SKIP_LOAD)) {   // measurement aid: MMAs run on whatever shared memory holds
                         if (cta_rank == 0) mbar_arrive(full_bar0 + 8 * stage);
                     } else if constexpr (CG == 2) {
                         // Both CTAs' copies complete on the LEADER's barrier.  Only the leader arrives on it,
@@ -393,13 +397,19 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         // cannot complete before that arrive).
                         const uint32_t bar = full_bar_leader + 8 * stage;
                         if (cta_rank == 0) mbar_arrive_expect_tx(full_bar0 + 8 * stage, 2 * T::STAGE_BYTES);
-                        tma_load_2d_pair(a_dst, &map_a, kb * T::TILE_K, m0, bar);
-                        tma_load_2d_pair(b_dst, &map_b, kb * T::TILE_K, nb, bar);
+#pragma unroll
+                        for (int a = 0; a < T::KATOMS; a++) {
+                            tma_load_2d_pair(a_dst + a * T::A_ATOM_BYTES, &map_a, kb * T::TILE_K + 128 * a, m0, bar);
+                            tma_load_2d_pair(b_dst + a * T::B_ATOM_BYTES, &map_b, kb * T::TILE_K + 128 * a, nb, bar);
+                        }
                     } else {
                         const uint32_t bar = full_bar0 + 8 * stage;
                         mbar_arrive_expect_tx(bar, T::STAGE_BYTES);
-                        tma_load_2d(a_dst, &map_a, kb * T::TILE_K, m0, bar);
-                        tma_load_2d(b_dst, &map_b, kb * T::TILE_K, nb, bar);
+#pragma unroll
+                        for (int a = 0; a < T::KATOMS; a++) {
+                            tma_load_2d(a_dst + a * T::A_ATOM_BYTES, &map_a, kb * T::TILE_K + 128 * a, m0, bar);
+                            tma_load_2d(b_dst + a * T::B_ATOM_BYTES, &map_b, kb * T::TILE_K + 128 * a, nb, bar);
+                        }
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -415,13 +425,16 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // ===== MMA issuer (leader CTA only) =====
         if (lane == 0 && cta_rank == 0) {
             const uint32_t idesc = make_idesc_e4m3_f32(T::TILE_M_CTA * CG, TN);
+            // Descriptors differ between stages only in the 14-bit start-address field.
+            const uint64_t adesc0 = make_kmajor_sw128_desc(base);
+            const uint64_t bdesc0 = make_kmajor_sw128_desc(base + T::A_BYTES);
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
             const bool prof = p.prof != nullptr;
-            long long t_full = 0, t_tmem = 0, n_tiles = 0;
+            long long t_full = 0, t_tmem = 0, n_tiles = 0, t_mma = 0, t_commit = 0;
             const long long t_begin = clock64();
             for (int tile = cluster_id; ok && tile < p.num_tiles; tile += num_clusters) {
                 wc.tile = tile;
@@ -432,22 +445,37 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * T::ACC_STRIDE;
                 for (int kb = 0; kb < p.k_blocks; kb++) {
-                    t0 = prof ? clock64() : 0;
+                    if (prof) t0 = clock64();
                     ok = wait_bar(full_bar0 + 8 * stage, phase, wc, ST_MMA_FULL_WAIT, stage);
                     if (prof) t_full += clock64() - t0;
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t a_src = base + stage * T::STAGE_BYTES;
-                    const uint64_t adesc = make_kmajor_sw128_desc(a_src);
-                    const uint64_t bdesc = make_kmajor_sw128_desc(a_src + T::A_BYTES);
-                    const int nmma = (kb == p.k_blocks - 1) ? p.last_kblock_mmas : 4;
+                    // Descriptors differ between stages, atoms and K steps only in the 14-bit start-address
+                    // field: +2 there = 32 bytes = one K = 32 step inside the 128-byte row.
+                    const uint32_t soff = static_cast<uint32_t>(stage) * (T::STAGE_BYTES >> 4);
+                    const uint64_t adesc = adesc0 + soff;
+                    const uint64_t bdesc = bdesc0 + soff;
+                    long long t1 = prof ? clock64() : 0;
+                    if (SL8_DBG(p.flags, DBG_SKIP_MMA)) {
+                        // measurement aid: stages are released at once, the loads run at their own pace
+                    } else if (kb < p.k_blocks - 1) {
 #pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        if (j < nmma)   // +2 in the address field = 32 bytes = one K step
-                            mma_f8<CG>(d_tmem, adesc + 2u * j, bdesc + 2u * j, idesc, (kb | j) != 0 ? 1u : 0u);
+                        for (int j = 0; j < 4 * T::KATOMS; j++) {
+                            const uint32_t o = (j >> 2) * (T::A_ATOM_BYTES >> 4) + 2 * (j & 3);
+                            const uint32_t ob = (j >> 2) * (T::B_ATOM_BYTES >> 4) + 2 * (j & 3);
+                            mma_f8<CG>(d_tmem, adesc + o, bdesc + ob, idesc, (j == 0 && kb == 0) ? 0u : 1u);
+                        }
+                    } else {
+                        for (int j = 0; j < p.last_kblock_mmas; j++) {
+                            const uint32_t o = (j >> 2) * (T::A_ATOM_BYTES >> 4) + 2 * (j & 3);
+                            const uint32_t ob = (j >> 2) * (T::B_ATOM_BYTES >> 4) + 2 * (j & 3);
+                            mma_f8<CG>(d_tmem, adesc + o, bdesc + ob, idesc, (kb | j) != 0 ? 1u : 0u);
+                        }
                     }
+                    if (prof) { const long long t2 = clock64(); t_mma += t2 - t1; t1 = t2; }
                     if constexpr (CG == 2) mma_commit_pair(empty_bar0 + 8 * stage, 0x3);
                     else mma_commit(empty_bar0 + 8 * stage);
+                    if (prof) t_commit += clock64() - t1;
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
@@ -462,6 +490,8 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 slot[PROF_MMA_WAIT_TMEM] = t_tmem;
                 slot[PROF_MMA_TOTAL] = clock64() - t_begin;
                 slot[PROF_TILES] = n_tiles;
+                slot[PROF_MMA_ISSUE] = t_mma;
+                slot[PROF_MMA_COMMIT] = t_commit;
             }
         }
         __syncwarp();
@@ -471,19 +501,76 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
         const int col_part = ew >> 2;              // 0, or 0/1 with eight epilogue warps
         const int col_begin = col_part * T::COLS_PER_WARP;
+        constexpr int RPT = T::REGIONS_PER_TILE;
+        constexpr bool HAS_BIAS = (OP != OP_PE);
+        constexpr bool HAS_SIDE = (OP != OP_FC1);
+        // Side values are fetched DIST regions ahead of their use; each region in flight owns one
+        // staging buffer and one more is being stored.
+        constexpr int DIST = HAS_SIDE ? (NBUF > 1 ? NBUF - 1 : 1) : 0;
+        static_assert(!HAS_SIDE || NBUF >= 2, "side data needs a buffer to land in while another is stored");
 
-        EpiRow e;
+        EpiCtx e;
         e.scale = (p.scale_a ? __ldg(p.scale_a) : 1.0f) * (p.scale_b ? __ldg(p.scale_b) : 1.0f);
         e.inv_out = __frcp_rn(p.out_scale ? __ldg(p.out_scale) : 1.0f);   // IEEE 1/x, as the CPU oracle computes it
         e.flags = p.flags;
         e.swz = lane & 7;
-        e.stage_row = lane * 128;
-        e.side_row = nullptr;
-        const uint32_t my_staging = staging_base + ew * T::STAGING_BUFS * T::REGION_BYTES;
-        uint32_t region_seq = 0;                   // staging regions used so far: selects the buffer
+        e.row_off = lane * 128;
+        const uint32_t my_staging = staging_base + ew * NBUF * T::REGION_BYTES;
+        const long long warp_row_in_tile = static_cast<long long>(cta_rank) * T::TILE_M_CTA + quad * 32;
 
-        constexpr bool HAS_BIAS = (OP != OP_PE);
-        constexpr bool HAS_SIDE = (OP != OP_FC1);
+        // --- side-data prefetch: region number `s` of this warp (RPT per tile, tiles in the order this
+        // cluster visits them) -> 32 rows x 128 bytes of the table / residual into staging buffer
+        // s % NBUF, in the swizzled layout the TMA store of the result expects; completion on that
+        // buffer's barrier.  One TMA load, except where the 32 rows wrap around the end of the
+        // periodic table (once per period): those are copied row by row.
+        const bool skip_side = SL8_DBG(p.flags, DBG_SKIP_SIDE);
+        const uint32_t my_side_bar = side_bar0 + 8 * ew * NBUF;
+        auto prefetch_side = [&](uint32_t s) {
+            const int tile = cluster_id + static_cast<int>(s / RPT) * num_clusters;
+            const uint32_t bar = my_side_bar + 8 * (s % NBUF);
+            const uint32_t buf = my_staging + (s % NBUF) * T::REGION_BYTES;
+            bool live = tile < p.num_tiles && !skip_side;
+            int col0 = 0;
+            long long m_w = 0;
+            if (live) {
+                const int tm = tile / p.tiles_n;
+                const int tn = tile - tm * p.tiles_n;
+                col0 = tn * TN + col_begin + static_cast<int>(s % RPT) * T::REGION_COLS;
+                m_w = static_cast<long long>(tm) * (T::TILE_M_CTA * CG) + warp_row_in_tile;
+                live = col0 < p.N;
+            }
+            if (!live) {
+                if (lane == 0) mbar_arrive(bar);
+                return;
+            }
+            int y = static_cast<int>(m_w);
+            bool wraps = false;
+            if constexpr (OP == OP_PE) {
+                y = static_cast<int>((static_cast<uint32_t>(m_w) + static_cast<uint32_t>(p.row_phase)) % static_cast<uint32_t>(p.period));
+                wraps = y + 32 > p.period;
+            }
+            if (!wraps) {
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(bar, T::REGION_BYTES);
+                    tma_load_2d(buf, &map_s, col0, y, bar);
+                }
+            } else {
+                const int piece = lane & 7;                 // 16-byte piece (8 bf16 columns) of the 128-byte row
+                const int col = col0 + piece * 8;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int r = (lane >> 3) + 4 * i;      // staging row 0..31
+                    int t = y + r;
+                    while (t >= p.period) t -= p.period;
+                    uint4 val = make_uint4(0, 0, 0, 0);
+                    if (col < p.N) val = __ldg(reinterpret_cast<const uint4*>(p.side + static_cast<long long>(t) * p.ld_side + col));
+                    sts128(buf + r * 128 + ((piece ^ (r & 7)) << 4), val.x, val.y, val.z, val.w);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar);
+            }
+        };
+
         constexpr int NB = T::COLS_PER_WARP / 32;  // bias values each lane stages per tile
         float* const bias_w = reinterpret_cast<float*>(base_ptr + (bias_base - base)) + ew * T::COLS_PER_WARP;
         float bnext[NB];
@@ -496,55 +583,37 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 __syncwarp();
             }
         }
+        if constexpr (HAS_SIDE) {
+#pragma unroll
+            for (int s = 0; s < DIST; s++) prefetch_side(s);
+        }
 
+        uint32_t seq = 0;                          // regions processed so far by this warp
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
         const bool prof = p.prof != nullptr && ew == 0;
-        long long t_acc = 0, t_store = 0, t_ld = 0;
+        long long t_acc = 0, t_store = 0, t_ld = 0, t_math = 0, t_issue = 0, t_refill = 0, t_pf = 0;
         const long long t_begin = clock64();
         for (int tile = cluster_id; tile < p.num_tiles; tile += num_clusters) {
             wc.tile = tile;
             const int tm = tile / p.tiles_n;
             const int tn = tile - tm * p.tiles_n;
-            const long long m_warp = static_cast<long long>(tm) * (T::TILE_M_CTA * CG) + cta_rank * T::TILE_M_CTA + quad * 32;
-            const long long row = m_warp + lane;
+            const long long m_warp = static_cast<long long>(tm) * (T::TILE_M_CTA * CG) + warp_row_in_tile;
             const int n0 = tn * TN;
 
-            // Work for the NEXT tile that can overlap this one: its bias (registers now, shared memory
-            // once this tile is done) and, for FC2, an L2 prefetch of this lane's residual row segment.
+            // The next tile's bias travels to registers while this tile is processed.
             const int next_tile = tile + num_clusters;
             const bool has_next = next_tile < p.num_tiles;
-            if (has_next && (HAS_BIAS || OP == OP_FC2)) {
-                const int ntm = next_tile / p.tiles_n;
-                const int ntn = next_tile - ntm * p.tiles_n;
-                if constexpr (HAS_BIAS) load_bias<NB>(bnext, p.bias, p.flags, ntn * TN + col_begin, lane, p.N);
-                if constexpr (OP == OP_FC2) {
-                    const long long nrow = static_cast<long long>(ntm) * (T::TILE_M_CTA * CG) + cta_rank * T::TILE_M_CTA + quad * 32 + lane;
-                    if (nrow < p.M && !(p.flags & DBG_SKIP_SIDE)) {
-                        const __nv_bfloat16* r = p.side + nrow * p.ld_side + ntn * TN + col_begin;
-#pragma unroll
-                        for (int j = 0; j < T::COLS_PER_WARP / 64; j++)
-                            if (ntn * TN + col_begin + 64 * j < p.N)
-                                asm volatile("prefetch.global.L2 [%0];" ::"l"(r + 64 * j));
-                    }
-                }
+            if constexpr (HAS_BIAS) {
+                if (has_next) load_bias<NB>(bnext, p.bias, p.flags, (next_tile % p.tiles_n) * TN + col_begin, lane, p.N);
             }
 
-            const bool row_ok = row < p.M;
-            e.out_row = row_ok ? static_cast<uint8_t*>(p.D) + static_cast<size_t>(row) * p.ldd * T::OUT_BYTES : nullptr;
-            if constexpr (OP == OP_PE)
-                e.side_row = row_ok ? p.side + ((row + p.row_phase) % p.period) * p.ld_side : nullptr;
-            else if constexpr (OP == OP_FC2)
-                e.side_row = row_ok ? p.side + row * p.ld_side : nullptr;
-            if (p.flags & DBG_SKIP_SIDE) e.side_row = nullptr;
-
-            // Side values of the first chunk are requested before the accumulator is waited for.
-            uint4 side_cur[4], side_nxt[4];
-            if constexpr (HAS_SIDE) load_side32(side_cur, e.side_row, n0 + col_begin, p.N);
-
+            // One lane polls; the others then confirm with a single try_wait of their own.
             long long t0 = prof ? clock64() : 0;
-            ok = wait_bar(tfull_bar0 + 8 * acc, acc_phase, wc, ST_EPI_TMEM_FULL_WAIT, acc);
+            if (lane == 0) ok = wait_bar(tfull_bar0 + 8 * acc, acc_phase, wc, ST_EPI_TMEM_FULL_WAIT, acc);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (ok && lane != 0) ok = wait_bar(tfull_bar0 + 8 * acc, acc_phase, wc, ST_EPI_TMEM_FULL_WAIT, acc);
             ok = __all_sync(0xffffffffu, ok);
             if (prof) t_acc += clock64() - t0;
             if (!ok) break;
@@ -552,88 +621,111 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * T::ACC_STRIDE;
             const bool warp_rows_ok = m_warp < p.M;      // warp-uniform: any row of this warp inside M
+            bool released = false;
 
 #pragma unroll 1
-            for (int c = col_begin; c < col_begin + T::COLS_PER_WARP; c += 32) {
-                const int col = n0 + c;
-                if (col >= p.N || (p.flags & DBG_SKIP_EPILOGUE)) break;   // warp-uniform: rest of the tile is past N
-                float v[32];
-                tmem_ld_32x32(t_row + c, v);
-                // next chunk's side values travel while this chunk is computed
+            for (int r = 0; r < RPT; r++, seq++) {
+                const int c0 = col_begin + r * T::REGION_COLS;       // first column of the region inside the tile
+                const int col0 = n0 + c0;
+                const uint32_t region = my_staging + (seq % NBUF) * T::REGION_BYTES;
+                if (prof) t0 = clock64();
                 if constexpr (HAS_SIDE) {
-                    if (c + 32 < col_begin + T::COLS_PER_WARP) load_side32(side_nxt, e.side_row, col + 32, p.N);
+                    // this region's side values have landed: one lane polls, the others confirm
+                    const uint32_t sbar = my_side_bar + 8 * (seq % NBUF);
+                    const uint32_t spar = (seq / NBUF) & 1u;
+                    if (lane == 0) ok = wait_bar(sbar, spar, wc, ST_EPI_SIDE_WAIT, seq % NBUF);
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (ok && lane != 0) ok = wait_bar(sbar, spar, wc, ST_EPI_SIDE_WAIT, seq % NBUF);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                } else {
+                    if (lane == 0) tma_store_wait_read<NBUF - 1>();   // the buffer is no longer read by an older store
+                    __syncwarp();
                 }
+                if (prof) t_store += clock64() - t0;
 
-                uint32_t region_base = 0;
-                int chunk16 = 0;
-                if constexpr (TMA_STORE) {
-                    const int in_region = (c - col_begin) % T::REGION_COLS;
-                    if (in_region == 0) {
-                        // The buffer about to be written must no longer be read by an earlier TMA store.
-                        t0 = prof ? clock64() : 0;
-                        if (lane == 0) tma_store_wait_read<T::STAGING_BUFS - 1>();
-                        __syncwarp();
-                        if (prof) t_store += clock64() - t0;
-                    }
-                    region_base = my_staging + (region_seq % T::STAGING_BUFS) * T::REGION_BYTES;
-                    chunk16 = in_region * T::OUT_BYTES / 16;
-                }
-                t0 = prof ? clock64() : 0;
-                tmem_ld_wait();
-                if (prof) t_ld += clock64() - t0;
-
-                const float* bias32 = bias_w + (c - col_begin);
-                epilogue_16<OP, OUT, TMA_STORE, 0>(v, e, bias32, side_cur[0], side_cur[1], col, region_base, chunk16);
-                if (col + 16 < p.N)
-                    epilogue_16<OP, OUT, TMA_STORE, 1>(v, e, bias32 + 16, side_cur[2], side_cur[3], col + 16, region_base,
-                                                       chunk16 + T::OUT_BYTES);
-                if constexpr (HAS_SIDE) {
+                const bool live = col0 < p.N && !SL8_DBG(p.flags, DBG_SKIP_EPILOGUE);   // warp-uniform
+                if (live) {
 #pragma unroll
-                    for (int i = 0; i < 4; i++) side_cur[i] = side_nxt[i];
-                }
-
-                if constexpr (TMA_STORE) {
-                    const int in_region = (c - col_begin) % T::REGION_COLS;
-                    const bool region_done = (in_region + 32 == T::REGION_COLS) || (col + 32 >= p.N);
-                    if (region_done && !(p.flags & DBG_SKIP_STORE)) {
+                    for (int ch = 0; ch < T::CHUNKS_PER_REGION; ch++) {
+                        const int c = c0 + 32 * ch;
+                        if (n0 + c < p.N) {
+                            float v[32];
+                            tmem_ld_32x32(t_row + c, v);
+                            if (prof) t0 = clock64();
+                            tmem_ld_wait();
+                            if (prof) t_ld += clock64() - t0;
+                            if (r == RPT - 1 && ch == T::CHUNKS_PER_REGION - 1) {
+                                // Last read of this accumulator: hand the TMEM buffer back before the math.
+                                tc_fence_before();
+                                __syncwarp();
+                                if (lane == 0) {
+                                    if constexpr (CG == 2) mbar_arrive_cluster(map_to_cta(tempty_bar0 + 8 * acc, 0));
+                                    else mbar_arrive(tempty_bar0 + 8 * acc);
+                                }
+                                released = true;
+                            }
+                            if (prof) t0 = clock64();
+                            const float* bias32 = bias_w + (c - col_begin);
+                            const int piece0 = ch * 2 * T::OUT_BYTES;            // 32 columns = 2 (e4m3) or 4 (bf16) pieces
+                            epilogue_16<OP, OUT, 0>(v, e, bias32, region, piece0);
+                            if (n0 + c + 16 < p.N) epilogue_16<OP, OUT, 1>(v, e, bias32 + 16, region, piece0 + T::OUT_BYTES);
+                            if (prof) t_math += clock64() - t0;
+                        }
+                    }
+                    if (prof) t0 = clock64();
+                    if (!SL8_DBG(p.flags, DBG_SKIP_STORE)) {
                         fence_proxy_async_smem();
                         __syncwarp();
-                        if (lane == 0 && warp_rows_ok) {
-                            tma_store_2d(&map_d, region_base, col - in_region, static_cast<int>(m_warp));
-                            tma_store_commit();
-                        }
-                        region_seq++;
+                        if (lane == 0 && warp_rows_ok) tma_store_2d(&map_d, region, col0, static_cast<int>(m_warp));
                     }
+                    if (prof) t_issue += clock64() - t0;
+                }
+                if (lane == 0) tma_store_commit();       // one bulk group per region, possibly empty
+                if constexpr (HAS_SIDE) {
+                    // Refill the buffer of the PREVIOUS region (its store may still be reading it) with the
+                    // side values of the region DIST ahead.
+                    if (prof) t0 = clock64();
+                    if (lane == 0) tma_store_wait_read<1>();
+                    __syncwarp();
+                    if (prof) { const long long t1 = clock64(); t_refill += t1 - t0; t0 = t1; }
+                    prefetch_side(seq + DIST);
+                    if (prof) t_pf += clock64() - t0;
                 }
             }
 
-            // The accumulator is in registers / on its way out: hand the TMEM buffer back.
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-                if constexpr (CG == 2) mbar_arrive_cluster(map_to_cta(tempty_bar0 + 8 * acc, 0));
-                else mbar_arrive(tempty_bar0 + 8 * acc);
+            if (!ok) break;
+            if (!released) {                             // tile whose last region lies past N
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    if constexpr (CG == 2) mbar_arrive_cluster(map_to_cta(tempty_bar0 + 8 * acc, 0));
+                    else mbar_arrive(tempty_bar0 + 8 * acc);
+                }
             }
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1u;
 
             if constexpr (HAS_BIAS) {
-                if (has_next) {   // every lane has finished reading this tile's bias (the __syncwarp above)
+                if (has_next) {
+                    __syncwarp();                        // every lane has finished reading this tile's bias
 #pragma unroll
                     for (int i = 0; i < NB; i++) bias_w[lane + 32 * i] = bnext[i];
                     __syncwarp();
                 }
             }
         }
-        if constexpr (TMA_STORE) {
-            if (lane == 0) tma_store_wait_all<0>();
-            __syncwarp();
-        }
+        if (lane == 0) tma_store_wait_all<0>();
+        __syncwarp();
         if (prof && lane == 0) {
             long long* slot = p.prof + static_cast<size_t>(blockIdx.x) * PROF_SLOTS;
             slot[PROF_EPI_WAIT_ACC] = t_acc;
             slot[PROF_EPI_WAIT_STORE] = t_store;
             slot[PROF_EPI_WAIT_LD] = t_ld;
+            slot[PROF_EPI_MATH] = t_math;
+            slot[PROF_EPI_STORE_ISSUE] = t_issue;
+            slot[PROF_EPI_REFILL] = t_refill;
+            slot[PROF_EPI_PREFETCH] = t_pf;
             slot[PROF_EPI_TOTAL] = clock64() - t_begin;
         }
     }

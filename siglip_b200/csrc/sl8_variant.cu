@@ -10,10 +10,10 @@
 namespace sl8 {
 namespace {
 
-template <int CG, int TN, int STAGES, int EW, int OP, int OUT, bool TS>
+template <int CG, int TN, int TK, int STAGES, int EW, int OP, int OUT, int NBUF>
 cudaError_t launch_one(const CUtensorMap* map_a, const CUtensorMap* map_b, const CUtensorMap* map_d,
-                       const KernelParams* params, int grid, cudaStream_t stream) {
-    using T = KernelTraits<CG, TN, STAGES, EW, OUT, TS>;
+                       const CUtensorMap* map_s, const KernelParams* params, int grid, cudaStream_t stream) {
+    using T = KernelTraits<CG, TN, TK, STAGES, EW, OUT, NBUF>;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
     cfg.blockDim = dim3(T::THREADS, 1, 1);
@@ -26,26 +26,33 @@ cudaError_t launch_one(const CUtensorMap* map_a, const CUtensorMap* map_b, const
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, sl8_gemm_kernel<CG, TN, STAGES, EW, OP, OUT, TS>, *map_a, *map_b, *map_d, *params);
+    return cudaLaunchKernelEx(&cfg, sl8_gemm_kernel<CG, TN, TK, STAGES, EW, OP, OUT, NBUF>, *map_a, *map_b, *map_d, *map_s, *params);
 }
 
-template <int ID, int CG, int TN, int STAGES, int EW, bool TS>
+// Kernel pointer / launcher of one layer, or nulls where the variant cannot serve it.
+template <int CG, int TN, int TK, int STAGES, int EW, int OP, int OUT, int NBUF, bool SERVED>
+struct Slot {
+    static const void* kernel() { return reinterpret_cast<const void*>(&sl8_gemm_kernel<CG, TN, TK, STAGES, EW, OP, OUT, NBUF>); }
+    static launch_fn launcher() { return &launch_one<CG, TN, TK, STAGES, EW, OP, OUT, NBUF>; }
+};
+template <int CG, int TN, int TK, int STAGES, int EW, int OP, int OUT, int NBUF>
+struct Slot<CG, TN, TK, STAGES, EW, OP, OUT, NBUF, false> {
+    static const void* kernel() { return nullptr; }
+    static launch_fn launcher() { return nullptr; }
+};
+
+template <int ID, int CG, int TN, int TK, int STAGES, int EW, int NBUF>
 const VariantEntry* make_entry() {
-    // A staging row holds 128 e4m3 columns; where a warp's column range is not a whole number of
-    // such regions (TN = 192) the e4m3 kernel stores from registers instead.
-    constexpr bool TS8 = TS && ((TN / (EW / 4)) % 128 == 0);
+    constexpr bool SIDE = NBUF >= 2;   // layers with side data need a second staging buffer
+    using T16 = KernelTraits<CG, TN, TK, STAGES, EW, OUT_BF16, NBUF>;
+    using T8 = KernelTraits<CG, TN, TK, STAGES, EW, OUT_E4M3, NBUF>;
     static const VariantEntry e = {
-        ID, CG, TN, STAGES, EW, TS ? 1 : 0,
-        KernelTraits<CG, TN, STAGES, EW, OUT_BF16, TS>::THREADS,
-        {TS ? 1 : 0, TS ? 1 : 0, TS8 ? 1 : 0, TS ? 1 : 0},
-        {KernelTraits<CG, TN, STAGES, EW, OUT_BF16, TS>::SMEM_BYTES, KernelTraits<CG, TN, STAGES, EW, OUT_BF16, TS>::SMEM_BYTES,
-         KernelTraits<CG, TN, STAGES, EW, OUT_E4M3, TS8>::SMEM_BYTES, KernelTraits<CG, TN, STAGES, EW, OUT_BF16, TS>::SMEM_BYTES},
-        {reinterpret_cast<const void*>(&sl8_gemm_kernel<CG, TN, STAGES, EW, OP_PE, OUT_BF16, TS>),
-         reinterpret_cast<const void*>(&sl8_gemm_kernel<CG, TN, STAGES, EW, OP_FC1, OUT_BF16, TS>),
-         reinterpret_cast<const void*>(&sl8_gemm_kernel<CG, TN, STAGES, EW, OP_FC1, OUT_E4M3, TS8>),
-         reinterpret_cast<const void*>(&sl8_gemm_kernel<CG, TN, STAGES, EW, OP_FC2, OUT_BF16, TS>)},
-        {&launch_one<CG, TN, STAGES, EW, OP_PE, OUT_BF16, TS>, &launch_one<CG, TN, STAGES, EW, OP_FC1, OUT_BF16, TS>,
-         &launch_one<CG, TN, STAGES, EW, OP_FC1, OUT_E4M3, TS8>, &launch_one<CG, TN, STAGES, EW, OP_FC2, OUT_BF16, TS>}};
+        ID, CG, TN, TK, STAGES, EW, NBUF, T16::THREADS,
+        {T16::SMEM_BYTES, T16::SMEM_BYTES, T8::SMEM_BYTES, T16::SMEM_BYTES},
+        {Slot<CG, TN, TK, STAGES, EW, OP_PE, OUT_BF16, NBUF, SIDE>::kernel(), Slot<CG, TN, TK, STAGES, EW, OP_FC1, OUT_BF16, NBUF, true>::kernel(),
+         Slot<CG, TN, TK, STAGES, EW, OP_FC1, OUT_E4M3, NBUF, true>::kernel(), Slot<CG, TN, TK, STAGES, EW, OP_FC2, OUT_BF16, NBUF, SIDE>::kernel()},
+        {Slot<CG, TN, TK, STAGES, EW, OP_PE, OUT_BF16, NBUF, SIDE>::launcher(), Slot<CG, TN, TK, STAGES, EW, OP_FC1, OUT_BF16, NBUF, true>::launcher(),
+         Slot<CG, TN, TK, STAGES, EW, OP_FC1, OUT_E4M3, NBUF, true>::launcher(), Slot<CG, TN, TK, STAGES, EW, OP_FC2, OUT_BF16, NBUF, SIDE>::launcher()}};
     return &e;
 }
 
@@ -55,14 +62,14 @@ const VariantEntry* make_entry() {
 #define SL8_CAT2(a, b) a##b
 #define SL8_CAT(a, b) SL8_CAT2(a, b)
 
-#define SL8_DEFINE_IF_SELECTED(id, CG, TN, ST, EW, TS)                                     \
+#define SL8_DEFINE_IF_SELECTED(id, CG, TN, TK, ST, EW, NB)                                     \
     template <int SEL, typename = void>                                                    \
     struct SL8_CAT(Pick, id) {                                                             \
         static const sl8::VariantEntry* get() { return nullptr; }                          \
     };                                                                                     \
     template <typename V>                                                                  \
     struct SL8_CAT(Pick, id)<id, V> {                                                      \
-        static const sl8::VariantEntry* get() { return sl8::make_entry<id, CG, TN, ST, EW, (TS) != 0>(); } \
+        static const sl8::VariantEntry* get() { return sl8::make_entry<id, CG, TN, TK, ST, EW, NB>(); } \
     };
 SL8_VARIANT_LIST(SL8_DEFINE_IF_SELECTED)
 #undef SL8_DEFINE_IF_SELECTED

@@ -178,7 +178,8 @@ class Engine:
 
     # ------------------------------------------------------------------ tracing
     TRACE_FIELDS = ("producer_wait", "producer_total", "mma_wait_operands", "mma_wait_accumulator", "mma_total",
-                    "epi_wait_accumulator", "epi_total", "epi_wait_store", "tiles", "epi_wait_tmem_load")
+                    "epi_wait_accumulator", "epi_total", "epi_wait_store", "tiles", "epi_wait_tmem_load",
+                    "epi_math", "epi_store_issue", "epi_refill", "epi_prefetch_issue", "mma_issue", "mma_commit")
 
     def trace_enable(self, on: bool = True) -> None:
         self._check(self._lib.sl8_trace_enable(self._h, 1 if on else 0))

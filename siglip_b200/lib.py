@@ -41,7 +41,7 @@ class SL8Error(RuntimeError):
 class Config(C.Structure):
     """Mirror of ``sl8_config``."""
     _fields_ = [(n, C.c_int) for n in ("cta_group", "tile_m", "tile_n", "tile_k", "stages", "epi_warps",
-                                       "tma_store", "grid", "smem_bytes", "variant_id")]
+                                       "staging_buffers", "grid", "smem_bytes", "variant_id")]
 
     def as_dict(self) -> dict:
         return {n: getattr(self, n) for n, _ in self._fields_}

@@ -31,8 +31,18 @@ CONFIGS = {
 
 
 def pitch16(k: int) -> int:
-    """Row pitch in bytes for K one-byte elements: TMA wants global strides in multiples of 16."""
+    """Smallest legal row pitch in bytes for K one-byte elements: TMA wants global strides in multiples of 16."""
     return (k + 15) // 16 * 16
+
+
+def pitch128(k: int) -> int:
+    """Row pitch that starts every row on a 128-byte line.  A TMA box row is 128 bytes; with a pitch that is
+    not a multiple of 128 each box row straddles two lines and the operand stream is measurably slower."""
+    return (k + 127) // 128 * 128
+
+
+# Row pitch rule used by the generators below for e4m3 operands (K contiguous).
+DEFAULT_PITCH = pitch128
 
 
 def quantize_e4m3(x: torch.Tensor, scale: Optional[float] = None, pitch: Optional[int] = None):
@@ -42,7 +52,7 @@ def quantize_e4m3(x: torch.Tensor, scale: Optional[float] = None, pitch: Optiona
         scale = amax / E4M3_MAX if amax > 0 else 1.0
     q = (x.float() / scale).clamp_(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn).view(torch.uint8)
     rows, k = q.shape
-    pitch = pitch16(k) if pitch is None else pitch
+    pitch = DEFAULT_PITCH(k) if pitch is None else pitch
     if pitch == k:
         return q.contiguous(), scale
     buf = torch.zeros((rows, pitch), dtype=torch.uint8, device=x.device)

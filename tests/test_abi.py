@@ -41,8 +41,8 @@ def test_version_and_variants(lib):
     for v in range(n):
         c = describe_variant(v)
         assert c["variant_id"] == v and c["cta_group"] in (1, 2) and c["tile_m"] == 128 * c["cta_group"]
-        assert c["tile_n"] in (128, 192, 256) and c["tile_k"] == 128 and c["smem_bytes"] <= 232448
-        seen.add((c["cta_group"], c["tile_n"], c["stages"], c["epi_warps"], c["tma_store"]))
+        assert c["tile_n"] in (128, 256) and c["tile_k"] in (128, 256) and c["smem_bytes"] <= 232448
+        seen.add((c["cta_group"], c["tile_n"], c["stages"], c["epi_warps"], c["staging_buffers"]))
     assert len(seen) == n
     with pytest.raises(Exception):
         describe_variant(n)

@@ -17,7 +17,9 @@ def test_quantize_matches_oracle(oracle):
     g = torch.Generator().manual_seed(0)
     x = torch.randn((64, 588), generator=g)
     q, s = synth.quantize_e4m3(x)
-    assert q.stride(0) == 592 and q.shape == (64, 588)
+    assert q.stride(0) == 640 and q.shape == (64, 588)      # rows start on 128-byte lines
+    q16, _ = synth.quantize_e4m3(x, pitch=synth.pitch16(588))
+    assert q16.stride(0) == 592 and torch.equal(q16, q)
     assert abs(s - float(x.abs().max()) / 448.0) < 1e-12
     want = np.array([[oracle.lib.sl8o_f32_to_e4m3(float(v)) for v in row] for row in (x / s).numpy()[:8]], dtype=np.uint8)
     assert np.array_equal(q.numpy()[:8], want)
@@ -28,7 +30,7 @@ def test_config_shapes():
     assert synth.CONFIGS["C1"]["M"] == 6272 and synth.CONFIGS["C2"]["M"] == 46656
     assert synth.CONFIGS["C4"]["M"] == 186624 and synth.CONFIGS["C4"]["K"] == 588
     p = synth.make_config("C4", images=2)
-    assert p.A.shape == (1458, 588) and p.A.stride(0) == 592 and p.table.shape == (729, 1152)
+    assert p.A.shape == (1458, 588) and p.A.stride(0) == 640 and p.table.shape == (729, 1152)
     assert p.flops() == 2.0 * 1458 * 1152 * 588
     p = synth.make_config("C3", images=1)
     assert p.residual.shape == (729, 1152) and p.bias.dtype == torch.bfloat16
