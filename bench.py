@@ -189,7 +189,9 @@ def launch_fn(eng, p, dev):
         Rs = [p.residual] + [p.residual.clone() for _ in range(sets - 1)]
         return (lambda i: eng.fc2_residual(As[i % sets], p.B, p.bias, Rs[i % sets], scale_a=sa, scale_b=sb,
                                            out=Ds[i % sets])), sets, Ds
-    return (lambda i: eng.patch_embed(As[i % sets], p.B, p.table, scale_a=sa, scale_b=sb, out=Ds[i % sets])), sets, Ds
+    table = eng.padded_table(p.table)            # rows past the period repeat it, as in the reference's padded table
+    return (lambda i: eng.patch_embed(As[i % sets], p.B, table, period=p.period, scale_a=sa, scale_b=sb,
+                                      out=Ds[i % sets])), sets, Ds
 
 
 def time_steps(fn, steps: int, warmup: int, barrier) -> float:
@@ -310,8 +312,8 @@ def main() -> None:
         e2e_fn = lambda: eng.fc2_residual_host(A_h, B_h, bias_h, side_h, D_h, scale_a=p.scale_a, scale_b=p.scale_b)
         side_bytes = bias_h.numel() * 2 + side_h.numel() * 2
     else:
-        side_h = p.table.cpu().pin_memory()
-        e2e_fn = lambda: eng.patch_embed_host(A_h, B_h, side_h, D_h, scale_a=p.scale_a, scale_b=p.scale_b)
+        side_h = eng.padded_table(p.table).cpu().pin_memory()
+        e2e_fn = lambda: eng.patch_embed_host(A_h, B_h, side_h, D_h, period=p.period, scale_a=p.scale_a, scale_b=p.scale_b)
         side_bytes = side_h.numel() * 2
     e2e_steps = max(3, min(args.steps, 10))
     e2e_fn()

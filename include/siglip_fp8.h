@@ -116,18 +116,38 @@ const char* sl8_version(void);
 
 /* Patch-embed GEMM + periodic table add.  Replaces persistent_gemm<BIAS_ADD>
  * (patch_embed.cu:200,216; epilogue patch_embed.cu:44-58; row -> table row
- * kernel_body.cuh:71).  `table` is bf16 [period, N] with leading dimension ld_table
- * (elements); the reference's table is bf16(bias + pos) (patch_embed.cu:79-98) -- the
- * caller folds the bias in the same way.  row_phase shifts the period for shards that
- * do not start on an image boundary: row m uses table row (m + row_phase) % period. */
+ * kernel_body.cuh:71).  `table` is bf16 [table_rows, N] with leading dimension ld_table
+ * (elements); row r holds bf16(bias + pos[r % period]) as the reference's table does
+ * (patch_embed.cu:79-98).  row_phase shifts the period for shards that do not start on an
+ * image boundary: row m uses table row (m + row_phase) % period.
+ * table_rows >= period.  Like the reference's table, which is padded to a multiple of 32 rows
+ * with rows that repeat its beginning (COMB_PADDED_ROWS, patch_embed.cu:17,87), the table may
+ * continue periodically past `period`; with table_rows >= period + 127 every 128-row tile of the
+ * output reads one contiguous block of table rows (fast path).  A table of exactly `period` rows
+ * is accepted and correct, but tiles that straddle its end are served by a slow copy loop.
+ * sl8_make_periodic_table / sl8_extend_periodic_table build a padded table. */
 int sl8_patch_embed_fp8(sl8_handle_t h,
                         const void* A, int64_t lda,
                         const void* B, int64_t ldb,
                         const float* scale_a, const float* scale_b,
-                        const void* table, int64_t ld_table, int period, int row_phase,
+                        const void* table, int64_t ld_table, int period, int table_rows, int row_phase,
                         void* D, int64_t ldd,
                         int64_t M, int N, int K,
                         unsigned flags, sl8_stream_t stream);
+
+/* Counterpart of the reference's precompute_combined kernel (patch_embed.cu:79-98), row-major:
+ * table[r, c] = bf16(bias[c] + pos[r % period, c]) for r < rows_out.  bias fp32 [N] (NULL = 0),
+ * pos fp32 [period, N] contiguous, table bf16 with leading dimension ld_table; all device
+ * pointers, caller-owned.  Use rows_out = sl8_padded_table_rows(period). */
+int sl8_make_periodic_table(sl8_handle_t h, const float* bias, const float* pos, int period, int N,
+                            void* table, int64_t ld_table, int rows_out, sl8_stream_t stream);
+
+/* Same for a table that already exists in bf16: out[r] = in[r % period], r < rows_out. */
+int sl8_extend_periodic_table(sl8_handle_t h, const void* table_in, int64_t ld_in, int period, int N,
+                              void* table_out, int64_t ld_out, int rows_out, sl8_stream_t stream);
+
+/* period + 127 rounded up to a multiple of 32: the row count of a padded table. */
+int sl8_padded_table_rows(int period);
 
 /* FC1 GEMM + bias + GELU(tanh).  Replaces persistent_gemm<BIAS_GELU>
  * (fc1_gelu.cu:131,147; gelu_fwd fc1_gelu.cu:16-19).  out_dtype SL8_OUT_BF16 writes
@@ -165,7 +185,7 @@ int sl8_fc2_residual_fp8(sl8_handle_t h,
 int sl8_patch_embed_fp8_host(sl8_handle_t h,
                              const void* A, int64_t lda, const void* B, int64_t ldb,
                              float scale_a, float scale_b,
-                             const void* table, int64_t ld_table, int period, int row_phase,
+                             const void* table, int64_t ld_table, int period, int table_rows, int row_phase,
                              void* D, int64_t ldd, int64_t M, int N, int K, unsigned flags);
 int sl8_fc1_gelu_fp8_host(sl8_handle_t h,
                           const void* A, int64_t lda, const void* B, int64_t ldb,

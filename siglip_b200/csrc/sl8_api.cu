@@ -120,7 +120,8 @@ int pick_variant(int op, int out_dtype, long long M, int N, int K) {
     // A tcgen05.mma of a CTA pair takes about 150 cycles whatever its N (measured for N = 128, 192,
     // 256), so the widest tile does the most work per instruction even where N = 1152 leaves the
     // fifth 256-wide tile half empty.
-    if (op == SL8_OP_FC1_GELU) return 2;   // GELU epilogue: two epilogue warps per scheduler
+    if (op == SL8_OP_FC1_GELU) return 2;      // GELU epilogue: two epilogue warps per scheduler
+    if (op == SL8_OP_PATCH_EMBED) return 5;   // short K: four staging boxes keep the table loads ahead of the epilogue
     return 1;
 }
 
@@ -133,7 +134,7 @@ struct Problem {
     const void* bias;
     const void* side;
     long long ld_side;
-    int period, row_phase;
+    int period, row_phase, table_rows;
     void* D;
     long long ldd;
     long long M;
@@ -159,6 +160,7 @@ int validate(sl8_handle_t h, const Problem& q) {
     if (q.op == SL8_OP_PATCH_EMBED) {
         if (!q.side) return fail(h, SL8_ERR_INVALID_VALUE, "table must not be NULL");
         if (q.period < 1 || q.row_phase < 0) return fail(h, SL8_ERR_INVALID_VALUE, "period must be positive, row_phase non-negative");
+        if (q.table_rows < q.period) return fail(h, SL8_ERR_INVALID_VALUE, "table_rows smaller than period");
         if (q.ld_side < q.N) return fail(h, SL8_ERR_INVALID_VALUE, "ld_table smaller than N");
         if (!aligned16(q.side) || (q.ld_side * 2) % 16) return fail(h, SL8_ERR_ALIGNMENT, "table must be 16-byte aligned with a 16-byte pitch");
     }
@@ -258,15 +260,15 @@ int run(sl8_handle_t h, const Problem& q, cudaStream_t stream) {
                    (unsigned)(128 / ob), 32, CU_TENSOR_MAP_L2_PROMOTION_NONE);
     if (rc != SL8_OK) return rc;
 
-    // Side data (table [period, N] or residual [M, N], bf16) comes in by TMA as 32-row x 64-column boxes.
+    // Side data (table [period, N] or residual [M, N], bf16) comes in by TMA as 128-row x 64-column boxes.
     CUtensorMap map_s = map_d;
     if (q.op == SL8_OP_PATCH_EMBED) {
         rc = encode_2d(h, &map_s, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, q.side, (unsigned long long)q.N,
-                       (unsigned long long)q.period, (unsigned long long)q.ld_side * 2, 64, 32, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+                       (unsigned long long)q.table_rows, (unsigned long long)q.ld_side * 2, 64, 128, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
         if (rc != SL8_OK) return rc;
     } else if (q.op == SL8_OP_FC2_RESIDUAL) {
         rc = encode_2d(h, &map_s, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, q.side, (unsigned long long)q.N,
-                       (unsigned long long)q.M, (unsigned long long)q.ld_side * 2, 64, 32, CU_TENSOR_MAP_L2_PROMOTION_NONE);
+                       (unsigned long long)q.M, (unsigned long long)q.ld_side * 2, 64, 128, CU_TENSOR_MAP_L2_PROMOTION_NONE);
         if (rc != SL8_OK) return rc;
     }
 
@@ -292,6 +294,7 @@ int run(sl8_handle_t h, const Problem& q, cudaStream_t stream) {
     p.ld_side = q.ld_side;
     p.period = q.period > 0 ? q.period : 1;
     p.row_phase = q.row_phase;
+    p.table_rows = q.table_rows;
     p.D = q.D;
     p.ldd = q.ldd;
     p.flags = q.flags;
@@ -418,13 +421,13 @@ SL8_API const char* sl8_last_error_string(sl8_handle_t h) {
 
 SL8_API int sl8_patch_embed_fp8(sl8_handle_t h, const void* A, int64_t lda, const void* B, int64_t ldb,
                                 const float* scale_a, const float* scale_b, const void* table, int64_t ld_table,
-                                int period, int row_phase, void* D, int64_t ldd, int64_t M, int N, int K,
+                                int period, int table_rows, int row_phase, void* D, int64_t ldd, int64_t M, int N, int K,
                                 unsigned flags, sl8_stream_t stream) {
     Problem q = {};
     q.op = SL8_OP_PATCH_EMBED; q.out_dtype = SL8_OUT_BF16;
     q.A = A; q.B = B; q.lda = lda; q.ldb = ldb;
     q.scale_a = scale_a; q.scale_b = scale_b;
-    q.side = table; q.ld_side = ld_table; q.period = period; q.row_phase = row_phase;
+    q.side = table; q.ld_side = ld_table; q.period = period; q.row_phase = row_phase; q.table_rows = table_rows;
     q.D = D; q.ldd = ldd; q.M = M; q.N = N; q.K = K; q.flags = flags;
     return run(h, q, static_cast<cudaStream_t>(stream));
 }
@@ -488,7 +491,7 @@ int run_host(sl8_handle_t h, Problem q, float scale_a, float scale_b, float out_
     if ((q.ldd * ob) % 16) return fail(h, SL8_ERR_ALIGNMENT, "row pitch of D must be a multiple of 16 bytes");
     const bool has_res = q.op == SL8_OP_FC2_RESIDUAL;
     if (has_res && (!q.side || q.ld_side < q.N || (q.ld_side * 2) % 16)) return fail(h, SL8_ERR_INVALID_VALUE, "bad residual");
-    if (q.op == SL8_OP_PATCH_EMBED && (!q.side || q.period < 1 || q.ld_side < q.N || (q.ld_side * 2) % 16 || q.row_phase < 0))
+    if (q.op == SL8_OP_PATCH_EMBED && (!q.side || q.period < 1 || q.table_rows < q.period || q.ld_side < q.N || (q.ld_side * 2) % 16 || q.row_phase < 0))
         return fail(h, SL8_ERR_INVALID_VALUE, "bad table");
 
     DeviceGuard guard(h->device);
@@ -520,7 +523,7 @@ int run_host(sl8_handle_t h, Problem q, float scale_a, float scale_b, float out_
     if ((rc = ensure(h, &pp.d_b, &pp.b_bytes, (size_t)q.N * q.ldb)) != SL8_OK) return rc;
     const size_t bias_need = (size_t)q.N * ((q.flags & SL8_FLAG_BIAS_F32) ? 4 : 2);
     if (q.bias && (rc = ensure(h, &pp.d_bias, &pp.bias_bytes, bias_need)) != SL8_OK) return rc;
-    if (q.op == SL8_OP_PATCH_EMBED && (rc = ensure(h, &pp.d_table, &pp.table_bytes, (size_t)q.period * q.ld_side * 2)) != SL8_OK) return rc;
+    if (q.op == SL8_OP_PATCH_EMBED && (rc = ensure(h, &pp.d_table, &pp.table_bytes, (size_t)q.table_rows * q.ld_side * 2)) != SL8_OK) return rc;
 
     // constants, once per call, on slot 0's stream
     cudaStream_t s0 = pp.stream[0];
@@ -528,7 +531,7 @@ int run_host(sl8_handle_t h, Problem q, float scale_a, float scale_b, float out_
     cudaMemcpyAsync(pp.d_scales, pp.h_scales, 12, cudaMemcpyHostToDevice, s0);
     cudaMemcpyAsync(pp.d_b, q.B, (size_t)q.N * q.ldb, cudaMemcpyHostToDevice, s0);
     if (q.bias) cudaMemcpyAsync(pp.d_bias, q.bias, bias_need, cudaMemcpyHostToDevice, s0);
-    if (q.op == SL8_OP_PATCH_EMBED) cudaMemcpyAsync(pp.d_table, q.side, (size_t)q.period * q.ld_side * 2, cudaMemcpyHostToDevice, s0);
+    if (q.op == SL8_OP_PATCH_EMBED) cudaMemcpyAsync(pp.d_table, q.side, (size_t)q.table_rows * q.ld_side * 2, cudaMemcpyHostToDevice, s0);
     e = cudaEventRecord(pp.consts_ready, s0);
     if (e != cudaSuccess) return fail_cuda(h, e, "upload of constants");
 
@@ -566,11 +569,12 @@ int run_host(sl8_handle_t h, Problem q, float scale_a, float scale_b, float out_
 
 SL8_API int sl8_patch_embed_fp8_host(sl8_handle_t h, const void* A, int64_t lda, const void* B, int64_t ldb,
                                      float scale_a, float scale_b, const void* table, int64_t ld_table, int period,
-                                     int row_phase, void* D, int64_t ldd, int64_t M, int N, int K, unsigned flags) {
+                                     int table_rows, int row_phase, void* D, int64_t ldd, int64_t M, int N, int K,
+                                     unsigned flags) {
     Problem q = {};
     q.op = SL8_OP_PATCH_EMBED; q.out_dtype = SL8_OUT_BF16;
     q.A = A; q.B = B; q.lda = lda; q.ldb = ldb;
-    q.side = table; q.ld_side = ld_table; q.period = period; q.row_phase = row_phase;
+    q.side = table; q.ld_side = ld_table; q.period = period; q.row_phase = row_phase; q.table_rows = table_rows;
     q.D = D; q.ldd = ldd; q.M = M; q.N = N; q.K = K; q.flags = flags;
     return run_host(h, q, scale_a, scale_b, 1.0f);
 }
@@ -690,4 +694,54 @@ SL8_API int sl8_trace_read(sl8_handle_t h, long long* out, int max_blocks) {
     e = cudaMemcpy(out, h->d_prof, sizeof(long long) * sl8::PROF_SLOTS * n, cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return fail_cuda(h, e, "read of the tracing buffer");
     return n;
+}
+
+// =========================================================================== periodic table
+
+namespace {
+
+__global__ void make_table_kernel(const float* __restrict__ bias, const float* __restrict__ pos, int period, int N,
+                                  __nv_bfloat16* __restrict__ table, long long ld, int rows) {
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= static_cast<long long>(rows) * N) return;
+    const int r = static_cast<int>(idx / N), c = static_cast<int>(idx % N);
+    const float b = bias ? bias[c] : 0.0f;
+    table[r * ld + c] = __float2bfloat16(b + pos[static_cast<long long>(r % period) * N + c]);   // patch_embed.cu:96
+}
+
+__global__ void extend_table_kernel(const __nv_bfloat16* __restrict__ in, long long ld_in, int period, int N,
+                                    __nv_bfloat16* __restrict__ out, long long ld_out, int rows) {
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= static_cast<long long>(rows) * N) return;
+    const int r = static_cast<int>(idx / N), c = static_cast<int>(idx % N);
+    out[r * ld_out + c] = in[static_cast<long long>(r % period) * ld_in + c];
+}
+
+}  // namespace
+
+SL8_API int sl8_padded_table_rows(int period) { return period < 1 ? 0 : (period + 127 + 31) / 32 * 32; }
+
+SL8_API int sl8_make_periodic_table(sl8_handle_t h, const float* bias, const float* pos, int period, int N, void* table,
+                                    int64_t ld_table, int rows_out, sl8_stream_t stream) {
+    if (!h) return SL8_ERR_INVALID_VALUE;
+    if (!pos || !table || period < 1 || N < 1 || rows_out < 1 || ld_table < N) return fail(h, SL8_ERR_INVALID_VALUE, "bad table arguments");
+    DeviceGuard guard(h->device);
+    const long long total = static_cast<long long>(rows_out) * N;
+    make_table_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        bias, pos, period, N, static_cast<__nv_bfloat16*>(table), ld_table, rows_out);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? SL8_OK : fail_cuda(h, e, "table kernel launch");
+}
+
+SL8_API int sl8_extend_periodic_table(sl8_handle_t h, const void* table_in, int64_t ld_in, int period, int N,
+                                      void* table_out, int64_t ld_out, int rows_out, sl8_stream_t stream) {
+    if (!h) return SL8_ERR_INVALID_VALUE;
+    if (!table_in || !table_out || period < 1 || N < 1 || rows_out < 1 || ld_in < N || ld_out < N)
+        return fail(h, SL8_ERR_INVALID_VALUE, "bad table arguments");
+    DeviceGuard guard(h->device);
+    const long long total = static_cast<long long>(rows_out) * N;
+    extend_table_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(table_in), ld_in, period, N, static_cast<__nv_bfloat16*>(table_out), ld_out, rows_out);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? SL8_OK : fail_cuda(h, e, "table kernel launch");
 }

@@ -19,6 +19,10 @@
 //                 values of a 32-row x 128-byte region are brought into that same staging buffer
 //                 by a TMA load a few regions ahead, added in place and stored from there.
 //
+//   last warp     side-data loader (patch-embed, FC2): one lane issues the TMA loads that bring the table /
+//                 residual regions into the epilogue warps' staging buffers as those become free, so
+//                 the epilogue warps never wait for a TMA instruction to be accepted.
+//
 // CG == 2 runs a CTA pair per tile (cluster of two, tcgen05 cta_group::2): each CTA loads its
 // own 128 rows of A and half of the tile's B rows, the leader issues 256 x TN MMAs that read
 // both CTAs' shared memory and write both CTAs' tensor memory.
@@ -57,7 +61,8 @@ enum : uint32_t {
     ST_MMA_FULL_WAIT = 2,
     ST_MMA_TMEM_EMPTY_WAIT = 3,
     ST_EPI_TMEM_FULL_WAIT = 4,
-    ST_EPI_SIDE_WAIT = 5
+    ST_EPI_SIDE_WAIT = 5,
+    ST_SIDE_LOADER_WAIT = 6
 };
 
 // Tracing slots written per CTA when KernelParams::prof is set (cycles, clock64).
@@ -97,6 +102,7 @@ struct KernelParams {
     long long ld_side;               // elements
     int period;
     int row_phase;
+    int table_rows;                  // rows the table holds: >= period; rows past period repeat it (patch-embed)
     void* D;
     long long ldd;                   // elements of the output type
     unsigned flags;
@@ -131,8 +137,8 @@ struct KernelTraits {
     static constexpr int REGIONS_PER_TILE = COLS_PER_WARP / REGION_COLS;
     static constexpr int CHUNKS_PER_REGION = REGION_COLS / 32;   // 32-column tcgen05.ld chunks per region
     static constexpr int BIAS_BYTES = EPI_WARPS * COLS_PER_WARP * 4;   // fp32 bias of the current tile, one copy per warp
-    static constexpr int THREADS = (2 + EPI_WARPS) * 32;
-    static constexpr int BAR_BYTES = 512;                        // pipeline barriers + one per staging buffer
+    static constexpr int THREADS = (3 + EPI_WARPS) * 32;         // producer, MMA, epilogue warps, side-data loader
+    static constexpr int BAR_BYTES = 512;                        // pipeline barriers + two per staging box
     static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STAGING_BYTES + BIAS_BYTES + BAR_BYTES;
     static_assert(STAGE_BYTES % 1024 == 0, "every operand tile must start on a swizzle-atom boundary");
     static_assert(COLS_PER_WARP % REGION_COLS == 0, "a warp stores whole staging regions");
@@ -174,14 +180,19 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, const Wa
 
 // tanh-form GELU of the reference (fc1_gelu.cu:16-19) written without the 1 + tanh
 // cancellation: 0.5 x (1 + tanh u) == x * sigmoid(2u) == x / (1 + exp(-2u)), with
-// u = sqrt(2/pi) (x + 0.044715 x^3).  Two SFU operations (ex2, rcp) per element.
-__device__ __forceinline__ float gelu_tanh_fast(float x) {
-    const float k2log2e = 2.0f * 0.7978845608f * 1.4426950408889634f;
-    const float x2 = x * x;
-    const float t = x * fmaf(k2log2e * 0.044715f, x2, k2log2e);  // 2 u log2(e)
-    float e;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-t));
-    return __fdividef(x, 1.0f + e);                               // rcp.approx + mul; x / inf == 0
+// u = sqrt(2/pi) (x + 0.044715 x^3).  Two SFU operations (ex2, rcp) per element; everything else
+// runs two elements per instruction on packed fp32 pairs.
+__device__ __forceinline__ uint64_t gelu_tanh_x2(uint64_t x) {
+    constexpr float K0 = -2.0f * 0.7978845608f * 1.4426950408889634f;   // -2 sqrt(2/pi) log2(e)
+    constexpr float K1 = K0 * 0.044715f;
+    const uint64_t x2 = mul_f32x2(x, x);
+    const uint64_t t = mul_f32x2(x, fma_f32x2(x2, pack_f32x2(K1, K1), pack_f32x2(K0, K0)));   // -2 u log2(e)
+    float t0, t1;
+    unpack_f32x2(t, t0, t1);
+    const uint64_t d = add_f32x2(pack_f32x2(ex2_approx(t0), ex2_approx(t1)), pack_f32x2(1.0f, 1.0f));
+    float d0, d1;
+    unpack_f32x2(d, d0, d1);
+    return mul_f32x2(x, pack_f32x2(rcp_approx(d0), rcp_approx(d1)));    // x / inf == 0
 }
 
 __device__ __forceinline__ void unpack8_bf16(const uint4& q, float (&f)[8]) {
@@ -235,9 +246,39 @@ __device__ __forceinline__ void epilogue_16(const float (&v)[32], const EpiCtx& 
 #pragma unroll
             for (int i = 0; i < 8; i++) w[i] = add_bf16x2(pack_bf16x2(x[2 * i], x[2 * i + 1]), tw[i]);
         }
-    } else {
-        // acc * scale + bias in one FMA; the bias comes from shared memory, the same address in every
-        // lane (a broadcast read).
+    } else if constexpr (OP == OP_FC1) {
+        // acc * scale + bias, GELU and the output scaling on packed fp32 pairs; the bias comes from shared
+        // memory, the same address in every lane (a broadcast read).
+        const uint64_t scale2 = pack_f32x2(e.scale, e.scale);
+        const uint64_t inv2 = pack_f32x2(e.inv_out, e.inv_out);
+        uint64_t g[8];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float4 b = *reinterpret_cast<const float4*>(bias16 + 4 * i);
+            g[2 * i + 0] = fma_f32x2(pack_f32x2(v[16 * H + 4 * i + 0], v[16 * H + 4 * i + 1]), scale2, pack_f32x2(b.x, b.y));
+            g[2 * i + 1] = fma_f32x2(pack_f32x2(v[16 * H + 4 * i + 2], v[16 * H + 4 * i + 3]), scale2, pack_f32x2(b.z, b.w));
+        }
+        if (!SL8_DBG(e.flags, DBG_SKIP_GELU)) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) g[i] = gelu_tanh_x2(g[i]);
+        }
+        if constexpr (OUT == OUT_BF16) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                float lo, hi;
+                unpack_f32x2(g[i], lo, hi);
+                w[i] = pack_bf16x2(lo, hi);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                float a, b, c, d;
+                unpack_f32x2(mul_f32x2(g[2 * i + 0], inv2), a, b);
+                unpack_f32x2(mul_f32x2(g[2 * i + 1], inv2), c, d);
+                w[i] = static_cast<uint32_t>(pack_e4m3x2(a, b)) | (static_cast<uint32_t>(pack_e4m3x2(c, d)) << 16);
+            }
+        }
+    } else {  // OP_FC2: (acc * scale + bias) + residual, fc2.cu:27-46
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const float4 b = *reinterpret_cast<const float4*>(bias16 + 4 * i);
@@ -246,31 +287,15 @@ __device__ __forceinline__ void epilogue_16(const float (&v)[32], const EpiCtx& 
             x[4 * i + 2] = fmaf(v[16 * H + 4 * i + 2], e.scale, b.z);
             x[4 * i + 3] = fmaf(v[16 * H + 4 * i + 3], e.scale, b.w);
         }
-        if constexpr (OP == OP_FC1) {
-            if (!SL8_DBG(e.flags, DBG_SKIP_GELU)) {
+        float r[8];
+        unpack8_bf16(lds128(a0), r);
 #pragma unroll
-                for (int i = 0; i < 16; i++) x[i] = gelu_tanh_fast(x[i]);
-            }
-        } else {  // OP_FC2: (acc + bias) + residual, fc2.cu:27-46
-            float r[8];
-            unpack8_bf16(lds128(a0), r);
+        for (int i = 0; i < 8; i++) x[i] += r[i];
+        unpack8_bf16(lds128(a1), r);
 #pragma unroll
-            for (int i = 0; i < 8; i++) x[i] += r[i];
-            unpack8_bf16(lds128(a1), r);
+        for (int i = 0; i < 8; i++) x[8 + i] += r[i];
 #pragma unroll
-            for (int i = 0; i < 8; i++) x[8 + i] += r[i];
-        }
-        if constexpr (OUT == OUT_BF16) {
-#pragma unroll
-            for (int i = 0; i < 8; i++) w[i] = pack_bf16x2(x[2 * i], x[2 * i + 1]);
-        } else {
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const uint32_t lo = pack_e4m3x2(x[4 * i + 0] * e.inv_out, x[4 * i + 1] * e.inv_out);
-                const uint32_t hi = pack_e4m3x2(x[4 * i + 2] * e.inv_out, x[4 * i + 3] * e.inv_out);
-                w[i] = lo | (hi << 16);
-            }
-        }
+        for (int i = 0; i < 8; i++) w[i] = pack_bf16x2(x[2 * i], x[2 * i + 1]);
     }
     sts128(a0, w[0], w[1], w[2], w[3]);
     if constexpr (OUT == OUT_BF16) sts128(a1, w[4], w[5], w[6], w[7]);
@@ -291,7 +316,7 @@ __device__ __forceinline__ void load_bias(float (&b)[NB], const void* bias, unsi
 }
 
 template <int CG, int TN, int TK, int STAGES, int EPI_WARPS, int OP, int OUT, int NBUF>
-__global__ void __launch_bounds__((2 + EPI_WARPS) * 32, 1)
+__global__ void __launch_bounds__((3 + EPI_WARPS) * 32, 1)
 sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_s,
                 const KernelParams p) {
@@ -314,8 +339,9 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     uint8_t* const bar_ptr = base_ptr + (bar_base - base);
     volatile uint32_t* const tmem_ptr = reinterpret_cast<volatile uint32_t*>(bar_ptr + 16 * STAGES + 32);
     volatile uint32_t* const abort_flag = tmem_ptr + 1;
-    const uint32_t side_bar0 = bar_base + 16 * STAGES + 48;     // EPI_WARPS * NBUF barriers: side data landed
-    static_assert(16 * STAGES + 48 + 8 * EPI_WARPS * NBUF <= T::BAR_BYTES, "barrier block too small");
+    const uint32_t side_bar0 = bar_base + 16 * STAGES + 48;     // (EPI_WARPS / 4) * NBUF barriers: side data landed
+    const uint32_t side_free0 = side_bar0 + 8 * (EPI_WARPS / 4) * NBUF;   // ... and: staging box reusable
+    static_assert(16 * STAGES + 48 + 16 * (EPI_WARPS / 4) * NBUF <= T::BAR_BYTES, "barrier block too small");
 
     const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
     const int lane = threadIdx.x & 31;
@@ -347,7 +373,10 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 mbar_init(tfull_bar0 + 8 * b, 1);                  // one tcgen05.commit
                 mbar_init(tempty_bar0 + 8 * b, EPI_WARPS * CG);    // one arrival per epilogue warp of the pair
             }
-            for (int b = 0; b < EPI_WARPS * NBUF; b++) mbar_init(side_bar0 + 8 * b, 1);   // one arrive per fill
+            for (int b = 0; b < (EPI_WARPS / 4) * NBUF; b++) {
+                mbar_init(side_bar0 + 8 * b, 1);     // one arrive (+ bytes) per fill of a group's box
+                mbar_init(side_free0 + 8 * b, 4);    // released by the group's four warps
+            }
             fence_mbar_init();
         }
         __syncwarp();
@@ -495,7 +524,7 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             }
         }
         __syncwarp();
-    } else {
+    } else if (warp < 2 + EPI_WARPS) {
         // ===== epilogue =====
         const int ew = warp - 2;
         const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
@@ -504,9 +533,6 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         constexpr int RPT = T::REGIONS_PER_TILE;
         constexpr bool HAS_BIAS = (OP != OP_PE);
         constexpr bool HAS_SIDE = (OP != OP_FC1);
-        // Side values are fetched DIST regions ahead of their use; each region in flight owns one
-        // staging buffer and one more is being stored.
-        constexpr int DIST = HAS_SIDE ? (NBUF > 1 ? NBUF - 1 : 1) : 0;
         static_assert(!HAS_SIDE || NBUF >= 2, "side data needs a buffer to land in while another is stored");
 
         EpiCtx e;
@@ -515,61 +541,13 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         e.flags = p.flags;
         e.swz = lane & 7;
         e.row_off = lane * 128;
-        const uint32_t my_staging = staging_base + ew * NBUF * T::REGION_BYTES;
+        // Staging is organised per column group (the four quadrant warps that cover the same columns):
+        // NBUF boxes of 128 rows x 128 bytes, of which this warp owns rows 32 * quad .. 32 * quad + 31.
+        const uint32_t my_staging = staging_base + col_part * NBUF * 4 * T::REGION_BYTES + quad * T::REGION_BYTES;
         const long long warp_row_in_tile = static_cast<long long>(cta_rank) * T::TILE_M_CTA + quad * 32;
 
-        // --- side-data prefetch: region number `s` of this warp (RPT per tile, tiles in the order this
-        // cluster visits them) -> 32 rows x 128 bytes of the table / residual into staging buffer
-        // s % NBUF, in the swizzled layout the TMA store of the result expects; completion on that
-        // buffer's barrier.  One TMA load, except where the 32 rows wrap around the end of the
-        // periodic table (once per period): those are copied row by row.
-        const bool skip_side = SL8_DBG(p.flags, DBG_SKIP_SIDE);
-        const uint32_t my_side_bar = side_bar0 + 8 * ew * NBUF;
-        auto prefetch_side = [&](uint32_t s) {
-            const int tile = cluster_id + static_cast<int>(s / RPT) * num_clusters;
-            const uint32_t bar = my_side_bar + 8 * (s % NBUF);
-            const uint32_t buf = my_staging + (s % NBUF) * T::REGION_BYTES;
-            bool live = tile < p.num_tiles && !skip_side;
-            int col0 = 0;
-            long long m_w = 0;
-            if (live) {
-                const int tm = tile / p.tiles_n;
-                const int tn = tile - tm * p.tiles_n;
-                col0 = tn * TN + col_begin + static_cast<int>(s % RPT) * T::REGION_COLS;
-                m_w = static_cast<long long>(tm) * (T::TILE_M_CTA * CG) + warp_row_in_tile;
-                live = col0 < p.N;
-            }
-            if (!live) {
-                if (lane == 0) mbar_arrive(bar);
-                return;
-            }
-            int y = static_cast<int>(m_w);
-            bool wraps = false;
-            if constexpr (OP == OP_PE) {
-                y = static_cast<int>((static_cast<uint32_t>(m_w) + static_cast<uint32_t>(p.row_phase)) % static_cast<uint32_t>(p.period));
-                wraps = y + 32 > p.period;
-            }
-            if (!wraps) {
-                if (lane == 0) {
-                    mbar_arrive_expect_tx(bar, T::REGION_BYTES);
-                    tma_load_2d(buf, &map_s, col0, y, bar);
-                }
-            } else {
-                const int piece = lane & 7;                 // 16-byte piece (8 bf16 columns) of the 128-byte row
-                const int col = col0 + piece * 8;
-#pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const int r = (lane >> 3) + 4 * i;      // staging row 0..31
-                    int t = y + r;
-                    while (t >= p.period) t -= p.period;
-                    uint4 val = make_uint4(0, 0, 0, 0);
-                    if (col < p.N) val = __ldg(reinterpret_cast<const uint4*>(p.side + static_cast<long long>(t) * p.ld_side + col));
-                    sts128(buf + r * 128 + ((piece ^ (r & 7)) << 4), val.x, val.y, val.z, val.w);
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar);
-            }
-        };
+        const uint32_t my_side_bar = side_bar0 + 8 * col_part * NBUF;      // side data of the group's box b landed
+        const uint32_t my_side_free = side_free0 + 8 * col_part * NBUF;    // the group's box b may be refilled
 
         constexpr int NB = T::COLS_PER_WARP / 32;  // bias values each lane stages per tile
         float* const bias_w = reinterpret_cast<float*>(base_ptr + (bias_base - base)) + ew * T::COLS_PER_WARP;
@@ -583,17 +561,12 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 __syncwarp();
             }
         }
-        if constexpr (HAS_SIDE) {
-#pragma unroll
-            for (int s = 0; s < DIST; s++) prefetch_side(s);
-        }
-
         uint32_t seq = 0;                          // regions processed so far by this warp
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
         const bool prof = p.prof != nullptr && ew == 0;
-        long long t_acc = 0, t_store = 0, t_ld = 0, t_math = 0, t_issue = 0, t_refill = 0, t_pf = 0;
+        long long t_acc = 0, t_store = 0, t_ld = 0, t_math = 0, t_issue = 0, t_refill = 0;
         const long long t_begin = clock64();
         for (int tile = cluster_id; tile < p.num_tiles; tile += num_clusters) {
             wc.tile = tile;
@@ -627,7 +600,7 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             for (int r = 0; r < RPT; r++, seq++) {
                 const int c0 = col_begin + r * T::REGION_COLS;       // first column of the region inside the tile
                 const int col0 = n0 + c0;
-                const uint32_t region = my_staging + (seq % NBUF) * T::REGION_BYTES;
+                const uint32_t region = my_staging + (seq % NBUF) * 4 * T::REGION_BYTES;
                 if (prof) t0 = clock64();
                 if constexpr (HAS_SIDE) {
                     // this region's side values have landed: one lane polls, the others confirm
@@ -683,14 +656,14 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 }
                 if (lane == 0) tma_store_commit();       // one bulk group per region, possibly empty
                 if constexpr (HAS_SIDE) {
-                    // Refill the buffer of the PREVIOUS region (its store may still be reading it) with the
-                    // side values of the region DIST ahead.
+                    // Once the PREVIOUS region's store has read its buffer, hand that buffer back to the
+                    // side-data loader (this region's store may still be reading its own).
                     if (prof) t0 = clock64();
-                    if (lane == 0) tma_store_wait_read<1>();
-                    __syncwarp();
-                    if (prof) { const long long t1 = clock64(); t_refill += t1 - t0; t0 = t1; }
-                    prefetch_side(seq + DIST);
-                    if (prof) t_pf += clock64() - t0;
+                    if (lane == 0) {
+                        tma_store_wait_read<1>();
+                        if (seq > 0) mbar_arrive(my_side_free + 8 * ((seq - 1) % NBUF));
+                    }
+                    if (prof) t_refill += clock64() - t0;
                 }
             }
 
@@ -725,9 +698,78 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             slot[PROF_EPI_MATH] = t_math;
             slot[PROF_EPI_STORE_ISSUE] = t_issue;
             slot[PROF_EPI_REFILL] = t_refill;
-            slot[PROF_EPI_PREFETCH] = t_pf;
             slot[PROF_EPI_TOTAL] = clock64() - t_begin;
         }
+    } else {
+        // ===== side-data loader =====
+        // Region number s of a column group (RPT per tile, tiles in the order this cluster visits them)
+        // -> 128 rows x 128 bytes of the table / residual (the rows of this CTA's tile, 64 bf16 columns)
+        // into the group's staging box s % NBUF, in the swizzled layout the TMA stores of the result
+        // expect; completion on the box's "landed" barrier.  One TMA load.  A positional table that holds
+        // at least period + 127 rows (rows past the period repeating it) never needs anything else; with
+        // an unpadded table the boxes that wrap around its end are copied row by row by the whole warp.
+        if constexpr (OP != OP_FC1) {
+            constexpr int RPT = T::REGIONS_PER_TILE;
+            constexpr int GROUPS = EPI_WARPS / 4;
+            constexpr uint32_t BOX_BYTES = 4 * T::REGION_BYTES;
+            const bool skip_side = SL8_DBG(p.flags, DBG_SKIP_SIDE);
+            int my_tiles = 0;
+            if (cluster_id < p.num_tiles) my_tiles = (p.num_tiles - cluster_id + num_clusters - 1) / num_clusters;
+            const uint32_t total = static_cast<uint32_t>(my_tiles) * RPT;
+            bool ok = true;
+            for (uint32_t s = 0; ok && s < total; s++) {
+                const int tile = cluster_id + static_cast<int>(s / RPT) * num_clusters;
+                const int tm = tile / p.tiles_n;
+                const int tn = tile - tm * p.tiles_n;
+                const long long m_cta = static_cast<long long>(tm) * (T::TILE_M_CTA * CG) + cta_rank * T::TILE_M_CTA;
+                wc.tile = tile;
+#pragma unroll 1
+                for (int g = 0; g < GROUPS; g++) {
+                    const uint32_t bsel = s % NBUF;
+                    const uint32_t landed = side_bar0 + 8 * (g * NBUF + bsel);
+                    const uint32_t freed = side_free0 + 8 * (g * NBUF + bsel);
+                    const uint32_t buf = staging_base + (g * NBUF + bsel) * BOX_BYTES;
+                    // the box's previous occupant (region s - NBUF) has been stored by all four warps
+                    if (lane == 0) ok = wait_bar(freed, ((s / NBUF) & 1u) ^ 1u, wc, ST_SIDE_LOADER_WAIT, g);
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) break;
+                    const int col0 = tn * TN + g * T::COLS_PER_WARP + static_cast<int>(s % RPT) * T::REGION_COLS;
+                    if (col0 >= p.N || skip_side) {
+                        if (lane == 0) mbar_arrive(landed);
+                        continue;
+                    }
+                    int y = static_cast<int>(m_cta);
+                    bool wraps = false;
+                    if constexpr (OP == OP_PE) {
+                        y = static_cast<int>((static_cast<uint32_t>(m_cta) + static_cast<uint32_t>(p.row_phase)) % static_cast<uint32_t>(p.period));
+                        wraps = y + T::TILE_M_CTA > p.table_rows;   // only a table without periodic padding wraps
+                    }
+                    if (!wraps) {
+                        if (lane == 0) {
+                            mbar_arrive_expect_tx(landed, BOX_BYTES);
+                            tma_load_2d(buf, &map_s, col0, y, landed);
+                        }
+                    } else {
+                        const int piece = lane & 7;                 // 16-byte piece (8 bf16 columns) of the 128-byte row
+                        const int col = col0 + piece * 8;
+                        int t = y + (lane >> 3);
+                        while (t >= p.period) t -= p.period;
+#pragma unroll 4
+                        for (int i = 0; i < 32; i++) {
+                            const int r = (lane >> 3) + 4 * i;      // staging row 0..127
+                            uint4 val = make_uint4(0, 0, 0, 0);
+                            if (col < p.N) val = __ldg(reinterpret_cast<const uint4*>(p.side + static_cast<long long>(t) * p.ld_side + col));
+                            sts128(buf + r * 128 + ((piece ^ (r & 7)) << 4), val.x, val.y, val.z, val.w);
+                            t += 4;
+                            while (t >= p.period) t -= p.period;
+                        }
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(landed);
+                    }
+                }
+            }
+        }
+        __syncwarp();
     }
 
     // ---------------------------------------------------------------- exit

@@ -30,9 +30,11 @@
     X(8, 2, 256, 128, 6, 4, 1)   \
     X(9, 2, 256, 256, 3, 4, 1)   \
     X(10, 2, 256, 256, 2, 4, 4)  \
-    X(11, 2, 256, 256, 2, 8, 2)
+    X(11, 2, 256, 256, 2, 8, 2)  \
+    X(12, 2, 256, 128, 3, 8, 3)  \
+    X(13, 2, 256, 128, 4, 4, 3)
 
-#define SL8_NUM_VARIANTS 12
+#define SL8_NUM_VARIANTS 14
 
 namespace sl8 {
 

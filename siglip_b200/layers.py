@@ -81,18 +81,42 @@ class Engine:
         return torch.empty((M, N), dtype=dtype, device=device)
 
     # ------------------------------------------------------------------ layers
-    def patch_embed(self, A, B, table, *, scale_a=None, scale_b=None, row_phase: int = 0, out=None,
-                    flags: int = 0, stream=None) -> torch.Tensor:
-        """D = bf16(bf16(sa*sb*A.B^T) + table[(m + row_phase) % period]); table is bf16 [period, N]."""
+    def patch_embed(self, A, B, table, *, period: Optional[int] = None, scale_a=None, scale_b=None, row_phase: int = 0,
+                    out=None, flags: int = 0, stream=None) -> torch.Tensor:
+        """D = bf16(bf16(sa*sb*A.B^T) + table[(m + row_phase) % period]).
+
+        ``table`` is bf16 [rows, N]; ``period`` defaults to its row count.  A table made by
+        :meth:`padded_table` (rows past the period repeat it) takes the fast path."""
         M, N, K = self._operands(A, B)
         if table.dtype != torch.bfloat16 or table.dim() != 2 or table.shape[1] != N or table.stride(1) != 1:
-            raise ValueError("table must be bf16 [period, N] with N contiguous")
+            raise ValueError("table must be bf16 [rows, N] with N contiguous")
+        period = table.shape[0] if period is None else int(period)
         D = self._new_out(M, N, torch.bfloat16, A.device) if out is None else out
         self._check(self._lib.sl8_patch_embed_fp8(
             self._h, A.data_ptr(), A.stride(0), B.data_ptr(), B.stride(0), _ptr(scale_a), _ptr(scale_b),
-            table.data_ptr(), table.stride(0), table.shape[0], int(row_phase), D.data_ptr(), D.stride(0),
+            table.data_ptr(), table.stride(0), period, table.shape[0], int(row_phase), D.data_ptr(), D.stride(0),
             M, N, K, int(flags), self._stream(stream)))
         return D
+
+    def padded_table(self, table: torch.Tensor, stream=None) -> torch.Tensor:
+        """bf16 [period, N] -> bf16 [sl8_padded_table_rows(period), N] whose extra rows repeat the period."""
+        period, N = table.shape
+        rows = self._lib.sl8_padded_table_rows(period)
+        out = torch.empty((rows, N), dtype=torch.bfloat16, device=table.device)
+        self._check(self._lib.sl8_extend_periodic_table(self._h, table.data_ptr(), table.stride(0), period, N,
+                                                        out.data_ptr(), out.stride(0), rows, self._stream(stream)))
+        return out
+
+    def make_table(self, bias: Optional[torch.Tensor], pos: torch.Tensor, stream=None) -> torch.Tensor:
+        """fp32 bias [N] (or None) and fp32 pos [period, N] -> padded bf16 table of bf16(bias + pos)."""
+        period, N = pos.shape
+        rows = self._lib.sl8_padded_table_rows(period)
+        out = torch.empty((rows, N), dtype=torch.bfloat16, device=pos.device)
+        pos = pos.contiguous().float()
+        b = None if bias is None else bias.contiguous().float()
+        self._check(self._lib.sl8_make_periodic_table(self._h, _ptr(b), pos.data_ptr(), period, N, out.data_ptr(),
+                                                      out.stride(0), rows, self._stream(stream)))
+        return out
 
     def fc1_gelu(self, A, B, bias, *, scale_a=None, scale_b=None, out_dtype=torch.bfloat16, out_scale=None,
                  out=None, flags: int = 0, stream=None) -> torch.Tensor:
@@ -126,12 +150,13 @@ class Engine:
         return D
 
     # ------------------------------------------------------------------ host operands
-    def patch_embed_host(self, A, B, table, out, *, scale_a=1.0, scale_b=1.0, row_phase=0, flags=0):
+    def patch_embed_host(self, A, B, table, out, *, period=None, scale_a=1.0, scale_b=1.0, row_phase=0, flags=0):
         M, K = A.shape
         N = B.shape[0]
+        period = table.shape[0] if period is None else int(period)
         self._check(self._lib.sl8_patch_embed_fp8_host(
             self._h, A.data_ptr(), A.stride(0), B.data_ptr(), B.stride(0), float(scale_a), float(scale_b),
-            table.data_ptr(), table.stride(0), table.shape[0], int(row_phase), out.data_ptr(), out.stride(0),
+            table.data_ptr(), table.stride(0), period, table.shape[0], int(row_phase), out.data_ptr(), out.stride(0),
             M, N, K, int(flags)))
         return out
 

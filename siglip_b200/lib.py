@@ -54,10 +54,13 @@ SIGNATURES = {
     "sl8_destroy": (_I, [_P]),
     "sl8_last_error_string": (C.c_char_p, [_P]),
     "sl8_version": (C.c_char_p, []),
-    "sl8_patch_embed_fp8": (_I, [_P, _P, _I64, _P, _I64, _P, _P, _P, _I64, _I, _I, _P, _I64, _I64, _I, _I, _U, _P]),
+    "sl8_patch_embed_fp8": (_I, [_P, _P, _I64, _P, _I64, _P, _P, _P, _I64, _I, _I, _I, _P, _I64, _I64, _I, _I, _U, _P]),
+    "sl8_make_periodic_table": (_I, [_P, _P, _P, _I, _I, _P, _I64, _I, _P]),
+    "sl8_extend_periodic_table": (_I, [_P, _P, _I64, _I, _I, _P, _I64, _I, _P]),
+    "sl8_padded_table_rows": (_I, [_I]),
     "sl8_fc1_gelu_fp8": (_I, [_P, _P, _I64, _P, _I64, _P, _P, _P, _P, _I64, _I, _P, _I64, _I, _I, _U, _P]),
     "sl8_fc2_residual_fp8": (_I, [_P, _P, _I64, _P, _I64, _P, _P, _P, _P, _I64, _P, _I64, _I64, _I, _I, _U, _P]),
-    "sl8_patch_embed_fp8_host": (_I, [_P, _P, _I64, _P, _I64, _F, _F, _P, _I64, _I, _I, _P, _I64, _I64, _I, _I, _U]),
+    "sl8_patch_embed_fp8_host": (_I, [_P, _P, _I64, _P, _I64, _F, _F, _P, _I64, _I, _I, _I, _P, _I64, _I64, _I, _I, _U]),
     "sl8_fc1_gelu_fp8_host": (_I, [_P, _P, _I64, _P, _I64, _F, _F, _P, _P, _I64, _I, _F, _I64, _I, _I, _U]),
     "sl8_fc2_residual_fp8_host": (_I, [_P, _P, _I64, _P, _I64, _F, _F, _P, _P, _I64, _P, _I64, _I64, _I, _I, _U]),
     "sl8_query_config": (_I, [_P, _I, _I, _I64, _I, _I, C.POINTER(Config)]),

@@ -53,10 +53,12 @@ def run_fc2(engine, oracle, M, N, K, seed):
     return check_bf16(bits(D), ref, f"fc2 {M}x{N}x{K}")
 
 
-def run_pe(engine, oracle, M, N, K, period, seed, row_phase=0, f32_add=False):
+def run_pe(engine, oracle, M, N, K, period, seed, row_phase=0, f32_add=False, padded=True):
     p = synth.make_patch_embed(M, N, K, period, seed=seed, device=DEV, pixels=True)
     fl = 2 if f32_add else 0
-    D = engine.patch_embed(p.A, p.B, p.table, scale_a=dscalar(p.scale_a), scale_b=dscalar(p.scale_b),
+    # padded: rows past the period repeat it (fast path); unpadded: tiles that straddle the end of the table
+    table = engine.padded_table(p.table) if padded else p.table
+    D = engine.patch_embed(p.A, p.B, table, period=period, scale_a=dscalar(p.scale_a), scale_b=dscalar(p.scale_b),
                            row_phase=row_phase, flags=fl)
     engine.device_status()
     ref = oracle.patch_embed(p.A.cpu().numpy(), p.B.cpu().numpy(), p.scale_a, p.scale_b, bits(p.table),
@@ -105,12 +107,28 @@ def test_patch_embed_fp32_add_mode(engine, oracle):
     run_pe(engine, oracle, 500, 768, 588, period=196, seed=6, row_phase=3, f32_add=True)
 
 
-def test_patch_embed_period_wrap(engine, oracle):
-    """Rows 195 / 196 / 197 and a period that is not a multiple of 32 (729)."""
-    run_pe(engine, oracle, 3 * 729 + 5, 1152, 588, period=729, seed=8)
+@pytest.mark.parametrize("padded", [True, False])
+def test_patch_embed_period_wrap(engine, oracle, padded):
+    """Rows 195 / 196 / 197 and a period that is not a multiple of 32 (729); with a table padded past the
+    period (fast path) and with one of exactly `period` rows (tiles that straddle its end)."""
+    run_pe(engine, oracle, 3 * 729 + 5, 1152, 588, period=729, seed=8, padded=padded)
+    run_pe(engine, oracle, 700, 768, 768, period=196, seed=9, row_phase=77, padded=padded)
 
 
-@pytest.mark.parametrize("vid", range(12))
+def test_periodic_table_helpers(engine):
+    """sl8_make_periodic_table is the reference's precompute_combined (patch_embed.cu:79-98) in row-major form."""
+    g = torch.Generator(device=DEV).manual_seed(0)
+    bias = torch.randn((768,), generator=g, device=DEV)
+    pos = torch.randn((196, 768), generator=g, device=DEV)
+    t = engine.make_table(bias, pos)
+    rows = t.shape[0]
+    assert rows >= 196 + 127 and rows % 32 == 0
+    want = (bias[None, :] + pos[torch.arange(rows, device=DEV) % 196]).to(torch.bfloat16)
+    assert torch.equal(t, want)
+    assert torch.equal(engine.padded_table(want[:196].contiguous()), want)
+
+
+@pytest.mark.parametrize("vid", range(13))
 def test_every_variant(engine, oracle, vid):
     assert vid < num_variants()
     engine.set_variant(vid)
@@ -167,7 +185,7 @@ def test_reference_known_answers_on_gpu(engine):
     bias = torch.arange(1, N + 1, dtype=torch.float32, device=DEV)
     pos = (3.0 * (torch.arange(196, dtype=torch.float32, device=DEV) + 1))[:, None].expand(196, N)
     table = (bias[None, :] + pos).to(torch.bfloat16).contiguous()
-    D = engine.patch_embed(ones(M, K), weights(N, K), table)
+    D = engine.patch_embed(ones(M, K), weights(N, K), engine.padded_table(table), period=196)
     acc = torch.where(torch.arange(N, device=DEV) % 2 == 1, 1.0, 1.5) * (K * 1.5)
     rows = torch.arange(M, device=DEV) % 196
     expect = (acc.to(torch.bfloat16).float()[None, :] + table.float()[rows]).to(torch.bfloat16)
