@@ -35,6 +35,12 @@ METRIC = "fp8_tflops_fc1_gelu"
 UNIT = "TFLOP/s"
 
 
+# DRAM bytes per GEMM row of the dominant kernel, from one `ncu --set full` capture per configuration on a
+# smaller case (profiles/*_ncu.md: dram__bytes_read.sum + dram__bytes_write.sum divided by the rows of the
+# captured launch).  Traffic grows in proportion to the rows, so a full launch is this figure times M.
+NCU_DRAM_BYTES_PER_ROW = {"C2": 321.59e6 / 37908, "C3": 327.73e6 / 37908, "C4": 169.39e6 / 75816}
+
+
 # ----------------------------------------------------------------------------- peaks
 def measured_peaks() -> dict:
     """Roofline denominators: the measured copy bandwidth and bf16 GEMM rate of this pool's B200s when
@@ -160,9 +166,11 @@ def reference_arm(args, rank: int, world: int) -> None:
     print(json.dumps(line), flush=True)
 
 
-def workload_config(name: str) -> dict:
+def workload_config(name: str, images=None) -> dict:
     from siglip_b200 import synth
-    c = synth.CONFIGS[name]
+    c = dict(synth.CONFIGS[name])
+    if images is not None:
+        c["M"], c["images"] = images * (c["M"] // c["images"]), images
     op = {0: "patch-embed + periodic table add", 1: "FC1 + bias + GELU(tanh)", 2: "FC2 + bias + residual"}[c["op"]]
     return {"workload": f"SigLIP {name}: {op}, M={c['M']} ({c['images']} images) K={c['K']} N={c['N']}, "
                         "e4m3 x e4m3 -> fp32 accumulate -> bf16, per-tensor scales",
@@ -241,6 +249,8 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--variant", type=int, default=-1, help="force a kernel variant (sweeps)")
+    ap.add_argument("--images", type=int, default=None, help="override the batch (profiling captures use a smaller case)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-operand leg (profiling captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -269,7 +279,8 @@ def main() -> None:
     eng = Engine(local_rank)
     if args.variant >= 0:
         eng.set_variant(args.variant)
-    p = synth.make_config(args.config, seed=rank, device=dev)
+    p = synth.make_config(args.config, seed=rank, device=dev, images=args.images)
+    n_images = synth.CONFIGS[args.config]["images"] if args.images is None else args.images
     fn, _, Ds = launch_fn(eng, p, dev)
     out_bytes = p.M * p.N * 2
 
@@ -296,65 +307,70 @@ def main() -> None:
     flops = p.flops()
     value = world * flops / ms_max / 1e9                      # TFLOP/s, all ranks
 
-    # ---- end to end: pinned host operands through the *_host entry point
-    A_h = torch.zeros((p.M, p.A.stride(0)), dtype=torch.uint8).pin_memory()[:, :p.K]
-    A_h.copy_(p.A)
-    B_h = p.B.cpu().pin_memory()
-    D_h = torch.empty((p.M, p.N), dtype=torch.bfloat16).pin_memory()
-    side_h = None
-    if p.op == synth.OP_FC1_GELU:
-        bias_h = p.bias.cpu().pin_memory()
-        e2e_fn = lambda: eng.fc1_gelu_host(A_h, B_h, bias_h, D_h, scale_a=p.scale_a, scale_b=p.scale_b)
-        side_bytes = bias_h.numel() * 2
-    elif p.op == synth.OP_FC2_RESIDUAL:
-        bias_h = p.bias.cpu().pin_memory()
-        side_h = p.residual.cpu().pin_memory()
-        e2e_fn = lambda: eng.fc2_residual_host(A_h, B_h, bias_h, side_h, D_h, scale_a=p.scale_a, scale_b=p.scale_b)
-        side_bytes = bias_h.numel() * 2 + side_h.numel() * 2
-    else:
-        side_h = eng.padded_table(p.table).cpu().pin_memory()
-        e2e_fn = lambda: eng.patch_embed_host(A_h, B_h, side_h, D_h, period=p.period, scale_a=p.scale_a, scale_b=p.scale_b)
-        side_bytes = side_h.numel() * 2
-    e2e_steps = max(3, min(args.steps, 10))
-    e2e_fn()
-    torch.cuda.synchronize()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_fn()                                              # blocking: returns when D is in host memory
-    e2e_ms = (time.perf_counter() - t0) / e2e_steps * 1e3
-    barrier()
-    t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_value = world * flops / float(t) / 1e9
-    same = torch.equal(D_h.to(dev).view(torch.uint16), Ds[0].view(torch.uint16)) if rank == 0 else True
+    e2e_value, e2e_ms_max, e2e_steps, same, side_bytes = None, None, 0, True, 0
+    if not args.no_e2e:
+        # ---- end to end: pinned host operands through the *_host entry point
+        A_h = torch.zeros((p.M, p.A.stride(0)), dtype=torch.uint8).pin_memory()[:, :p.K]
+        A_h.copy_(p.A)
+        B_h = p.B.cpu().pin_memory()
+        D_h = torch.empty((p.M, p.N), dtype=torch.bfloat16).pin_memory()
+        side_h = None
+        if p.op == synth.OP_FC1_GELU:
+            bias_h = p.bias.cpu().pin_memory()
+            e2e_fn = lambda: eng.fc1_gelu_host(A_h, B_h, bias_h, D_h, scale_a=p.scale_a, scale_b=p.scale_b)
+            side_bytes = bias_h.numel() * 2
+        elif p.op == synth.OP_FC2_RESIDUAL:
+            bias_h = p.bias.cpu().pin_memory()
+            side_h = p.residual.cpu().pin_memory()
+            e2e_fn = lambda: eng.fc2_residual_host(A_h, B_h, bias_h, side_h, D_h, scale_a=p.scale_a, scale_b=p.scale_b)
+            side_bytes = bias_h.numel() * 2 + side_h.numel() * 2
+        else:
+            side_h = eng.padded_table(p.table).cpu().pin_memory()
+            e2e_fn = lambda: eng.patch_embed_host(A_h, B_h, side_h, D_h, period=p.period, scale_a=p.scale_a, scale_b=p.scale_b)
+            side_bytes = side_h.numel() * 2
+        e2e_steps = max(3, min(args.steps, 10))
+        e2e_fn()
+        torch.cuda.synchronize()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_fn()                                              # blocking: returns when D is in host memory
+        e2e_ms = (time.perf_counter() - t0) / e2e_steps * 1e3
+        barrier()
+        t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms_max = float(t)
+        e2e_value = world * flops / e2e_ms_max / 1e9
+        same = torch.equal(D_h.to(dev).view(torch.uint16), Ds[0].view(torch.uint16)) if rank == 0 else True
 
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_max, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "e4m3 x e4m3 -> f32", "data": "synthetic", "config": workload_config(args.config),
+            "dtype": "e4m3 x e4m3 -> f32", "data": "synthetic", "config": workload_config(args.config, args.images),
             "clocks": clocks, "gpu_launches": args.steps,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(p.M * p.A.stride(0) + p.N * p.B.stride(0) + side_bytes + 12),
-                    "d2h_bytes_per_step": int(out_bytes), "ms_per_step": float(t), "steps": e2e_steps,
+                    "d2h_bytes_per_step": int(out_bytes), "ms_per_step": e2e_ms_max, "steps": e2e_steps,
                     "matches_device_path": bool(same)},
-            "images_per_s": world * synth.CONFIGS[args.config]["images"] / ms_max * 1e3,
+            "images_per_s": world * n_images / ms_max * 1e3,
             "kernel_config": eng.query_config(p.op, p.M, p.N, p.K),
         }
         tensor_bound = p.op != synth.OP_PATCH_EMBED
         per_gpu_tf = flops / ms / 1e9
         per_gpu_gbs = p.min_bytes() / ms / 1e6
+        per_row = NCU_DRAM_BYTES_PER_ROW.get(args.config)
+        traffic = None if per_row is None else per_row * p.M
         if tensor_bound:
             peak = 2.0 * peaks["bf16_tflops"]
             line["roofline"] = {"bound": "tensor", "achieved": per_gpu_tf, "peak": peak, "unit": "TFLOP/s",
-                                "frac": per_gpu_tf / peak, "traffic": None,
+                                "frac": per_gpu_tf / peak, "traffic": traffic,
                                 "peak_source": f"2 x bf16 burst GEMM rate of {peaks['source']} MEASURED_PEAKS (e4m3 MMA rate is twice bf16)",
                                 "frac_of_nominal_4500": per_gpu_tf / 4500.0,
                                 "hbm_gbs_algorithmic": per_gpu_gbs}
         else:
             line["roofline"] = {"bound": "hbm", "achieved": per_gpu_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                "frac": per_gpu_gbs / peaks["hbm_gbs"], "traffic": None,
+                                "frac": per_gpu_gbs / peaks["hbm_gbs"], "traffic": traffic,
                                 "peak_source": f"{peaks['source']} copy bandwidth", "tflops": per_gpu_tf}
         if not args.no_cpu_baseline:
             v, cores, sample, secs = cpu_oracle_rate(args.config, args.cpu_seconds)
