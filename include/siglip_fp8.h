@@ -247,6 +247,40 @@ int sl8_set_wait_budget_ms(sl8_handle_t h, int ms);
 int sl8_trace_enable(sl8_handle_t h, int on);
 int sl8_trace_read(sl8_handle_t h, long long* out, int max_blocks);
 
+/* ---- FC1 without any device allocation ---------------------------------------------------
+ * No counterpart in the reference (its hosts allocate every buffer in main()).
+ *
+ * For callers that are not allowed to allocate device memory -- a plug-in's enqueue callback, a
+ * serving loop whose memory pool was frozen at start-up, a process living inside a fixed device
+ * memory budget -- and therefore cannot call sl8_create (its handle owns a cudaMalloc'ed status
+ * block) or sl8_trace_enable.  Same kernel and arithmetic as sl8_fc1_gelu_fp8; the status block and
+ * the trace records live in a __device__ array inside the library image instead
+ * (SL8_STATIC_SCRATCH_BYTES per GPU that loads the library, held until the process exits).
+ * The call allocates nothing and needs no handle; it runs on the CURRENT device.
+ *
+ *   host_status  optional, 4 words of host memory: receives the status block (word 0 != 0: a device
+ *                wait expired; see sl8_device_status) by a copy enqueued on `stream` after the kernel;
+ *   host_trace   optional, room for SL8_TRACE_SLOTS x (return value) 64-bit counters: switches
+ *                tracing on for this launch and receives one record per CTA the same way.
+ * Both are valid once `stream` has been synchronised.
+ *
+ * Returns the number of CTAs launched (> 0) or a negative status code.  A launch of more than
+ * SL8_STATIC_MAX_CTAS CTAs does not fit the scratch and is refused with SL8_ERR_UNSUPPORTED; flags
+ * other than SL8_FLAG_BIAS_F32 are refused with SL8_ERR_INVALID_VALUE.
+ *
+ * All calls on one GPU share the one array, which keeps what the previous call left in it: the status
+ * block is cleared on `stream` before every launch, and calls that overlap on the GPU (different
+ * streams) race on it -- keep them on one stream.  The first call on a device looks up the array's
+ * device address and prepares the kernel (no allocation); make that first call before any stream
+ * capture begins. */
+#define SL8_STATIC_MAX_CTAS 512
+#define SL8_STATIC_SCRATCH_BYTES (256 + SL8_STATIC_MAX_CTAS * SL8_TRACE_SLOTS * 8)
+int sl8_fc1_gelu_fp8_static(const void* A, int64_t lda, const void* B, int64_t ldb,
+                            const float* scale_a, const float* scale_b, const void* bias,
+                            void* D, int64_t ldd, int out_dtype, const float* out_scale,
+                            int64_t M, int N, int K, unsigned flags,
+                            unsigned* host_status, long long* host_trace, sl8_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

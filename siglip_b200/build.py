@@ -80,9 +80,10 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         objs.append(o)
         jobs.append(([exe, *NVCC_FLAGS, f"-DSL8_VARIANT_ID={vid}", "-c", str(CSRC / "sl8_variant.cu"), "-o", str(o)],
                      OBJ / f"variant_{vid}.log", verbose))
-    o = OBJ / "api.o"
-    objs.append(o)
-    jobs.append(([exe, *NVCC_FLAGS, "-c", str(CSRC / "sl8_api.cu"), "-o", str(o)], OBJ / "api.log", verbose))
+    for name in ("api", "static"):
+        o = OBJ / f"{name}.o"
+        objs.append(o)
+        jobs.append(([exe, *NVCC_FLAGS, "-c", str(CSRC / f"sl8_{name}.cu"), "-o", str(o)], OBJ / f"{name}.log", verbose))
     with cf.ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 4)) as pool:
         list(pool.map(compile_one, jobs))
     link = [exe, *ARCH_FLAGS, "-shared", "-o", str(LIB), *map(str, objs), "-cudart", "static"]

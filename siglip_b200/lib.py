@@ -71,6 +71,7 @@ SIGNATURES = {
     "sl8_set_wait_budget_ms": (_I, [_P, _I]),
     "sl8_trace_enable": (_I, [_P, _I]),
     "sl8_trace_read": (_I, [_P, C.POINTER(C.c_longlong), _I]),
+    "sl8_fc1_gelu_fp8_static": (_I, [_P, _I64, _P, _I64, _P, _P, _P, _P, _I64, _I, _P, _I64, _I, _I, _U, _P, _P, _P]),
 }
 
 
