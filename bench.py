@@ -219,11 +219,40 @@ def time_steps(fn, steps: int, warmup: int, barrier) -> float:
     return e0.elapsed_time(e1) / steps
 
 
-def layer_table(eng, dev, steps: int, peaks: dict) -> dict:
-    """Per-layer numbers for the other configurations (C1, C3, C4), same timing protocol."""
+def cublaslt_baseline(p, dev, steps: int) -> dict:
+    """cuBLASLt per-tensor-scaled FP8 GEMM on the same operands (through torch._scaled_mm), as the reference's
+    bench/cublas_bench.cu times it: GEMM alone (bias fused where the layer has one) and GEMM followed by the
+    layer's epilogue as separate elementwise kernels.  K is taken at the operands' row pitch (the padding is
+    zero), because cuBLASLt wants K % 16 == 0."""
+    from siglip_b200 import synth
+    try:
+        kp = p.A.stride(0)
+        A = torch.as_strided(p.A, (p.M, kp), (kp, 1)).view(torch.float8_e4m3fn)
+        B = torch.as_strided(p.B, (p.N, kp), (kp, 1)).view(torch.float8_e4m3fn)
+        sa = torch.tensor(p.scale_a, device=dev, dtype=torch.float32)
+        sb = torch.tensor(p.scale_b, device=dev, dtype=torch.float32)
+        bias = p.bias if p.op != synth.OP_PATCH_EMBED else None
+        gemm = lambda i=0: torch._scaled_mm(A, B.t(), scale_a=sa, scale_b=sb, bias=bias, out_dtype=torch.bfloat16)
+        if p.op == synth.OP_FC1_GELU:
+            full = lambda i=0: torch.nn.functional.gelu(gemm(), approximate="tanh")
+        elif p.op == synth.OP_FC2_RESIDUAL:
+            full = lambda i=0: gemm().add_(p.residual)
+        else:
+            imgs = p.M // p.period
+            full = lambda i=0: gemm().view(imgs, p.period, p.N).add_(p.table)
+        t_gemm = time_steps(gemm, steps, 3, lambda: None)
+        t_full = time_steps(full, steps, 3, lambda: None)
+        return {"cublaslt_gemm_ms": t_gemm, "cublaslt_gemm_tflops": p.flops() / t_gemm / 1e9,
+                "cublaslt_unfused_ms": t_full, "cublaslt_unfused_tflops": p.flops() / t_full / 1e9}
+    except Exception as e:          # a torch build without _scaled_mm for this shape: report, do not fail the bench
+        return {"cublaslt_error": f"{type(e).__name__}: {str(e)[:160]}"}
+
+
+def layer_table(eng, dev, steps: int, peaks: dict, names=("C1", "C2", "C3", "C4")) -> dict:
+    """Per-layer numbers for every configuration with the same timing protocol, beside cuBLASLt FP8."""
     from siglip_b200 import synth
     out = {}
-    for name in ("C1", "C3", "C4"):
+    for name in names:
         p = synth.make_config(name, seed=0, device=dev)
         fn, _, _ = launch_fn(eng, p, dev)
         ms = time_steps(fn, steps, 3, lambda: None)
@@ -233,9 +262,59 @@ def layer_table(eng, dev, steps: int, peaks: dict) -> dict:
         out[name] = {"ms": ms, "tflops": tf, "gbs": gbs, "frac_fp8_measured": tf / (2 * peaks["bf16_tflops"]),
                      "frac_hbm_measured": gbs / peaks["hbm_gbs"], "frac_fp8_nominal_4500": tf / 4500.0,
                      "images_per_s": synth.CONFIGS[name]["images"] / ms * 1e3}
-        del p, fn
+        del fn
+        torch.cuda.empty_cache()
+        out[name].update(cublaslt_baseline(p, dev, steps))
+        del p
         torch.cuda.empty_cache()
     return out
+
+
+def chain_bench(args, eng, dev, rank: int, world: int, barrier, dist) -> None:
+    """C5: the MLP chain FC1 + GELU -> e4m3 -> FC2 + residual on this rank's share of 1024 images (M = 746 496
+    rows in total; strong scaling: the images are divided over the ranks, no data crosses GPUs)."""
+    from siglip_b200 import synth
+    from siglip_b200.shard import image_range
+    total_images = 1024 if args.images is None else args.images
+    _, n_img = image_range(total_images, world, rank)
+    M = n_img * 729
+    d_model, d_ff = 1152, 4304
+    p1 = synth.make_fc1(M, d_ff, d_model, seed=rank, device=dev)
+    w2 = synth.make_fc2(729, d_model, d_ff, seed=rank, device=dev)          # FC2 weights and bias
+    g = torch.Generator(device=dev).manual_seed(1000 + rank)
+    residual = torch.randn((M, d_model), generator=g, device=dev).to(torch.bfloat16)
+    sa1, sb1 = torch.tensor([p1.scale_a], device=dev), torch.tensor([p1.scale_b], device=dev)
+    sb2 = torch.tensor([w2.scale_b], device=dev)
+    # static activation scale of the hidden layer: amax / 448 of a one-image calibration pass
+    cal = eng.fc1_gelu(p1.A[:729], p1.B, p1.bias, scale_a=sa1, scale_b=sb1)
+    h_scale = torch.tensor([float(cal.float().abs().max()) / 448.0], device=dev)
+    H = torch.empty((M, synth.pitch128(d_ff)), dtype=torch.uint8, device=dev)[:, :d_ff]
+    D = torch.empty((M, d_model), dtype=torch.bfloat16, device=dev)
+
+    def step(i):
+        eng.fc1_gelu(p1.A, p1.B, p1.bias, scale_a=sa1, scale_b=sb1, out=H, out_dtype=torch.uint8, out_scale=h_scale)
+        eng.fc2_residual(H, w2.B, w2.bias, residual, scale_a=h_scale, scale_b=sb2, out=D)
+
+    ms = time_steps(step, args.steps, args.warmup, barrier)
+    eng.device_status()
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t)
+    flops = 2.0 * 2.0 * total_images * 729 * d_ff * d_model
+    if rank == 0:
+        peaks = measured_peaks()
+        tf = flops / ms_max / 1e9
+        print(json.dumps({
+            "metric": "fp8_tflops_mlp_chain", "value": tf, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_max, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32", "data": "synthetic",
+            "config": {"workload": f"SigLIP C5: MLP chain FC1+GELU (e4m3 out) -> FC2+residual, {total_images} images "
+                                   f"(M={total_images * 729}) split by image over {world} GPU(s), K/N 1152/4304",
+                       "l2": "operands of one step (> 7 GB at 1 GPU) exceed the 126 MB L2"},
+            "images_per_s": total_images / ms_max * 1e3, "gpu_launches": 2 * args.steps,
+            "roofline": {"bound": "tensor", "achieved": tf / world, "peak": 2.0 * peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": tf / world / (2.0 * peaks["bf16_tflops"]), "traffic": None}}), flush=True)
 
 
 def main() -> None:
@@ -244,7 +323,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="C2", choices=["C1", "C2", "C3", "C4"])
+    ap.add_argument("--config", default="C2", choices=["C1", "C2", "C3", "C4", "C5"])
     ap.add_argument("--layers", action="store_true", help="also time C1, C3 and C4 and add them under 'layers'")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
@@ -279,6 +358,12 @@ def main() -> None:
     eng = Engine(local_rank)
     if args.variant >= 0:
         eng.set_variant(args.variant)
+    if args.config == "C5":
+        chain_bench(args, eng, dev, rank, world, barrier, dist)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     p = synth.make_config(args.config, seed=rank, device=dev, images=args.images)
     n_images = synth.CONFIGS[args.config]["images"] if args.images is None else args.images
     fn, _, Ds = launch_fn(eng, p, dev)

@@ -113,9 +113,10 @@ int pick_variant(int op, int out_dtype, long long M, int N, int K) {
     (void)K;
     (void)N;
     const long long tiles256 = ((M + 255) / 256) * ((N + 255) / 256);
-    if (tiles256 < 74) {
-        // Too few 256 x 256 tiles to fill the GPU: smaller tiles give more of the 148 SMs work.
-        return (M <= 128) ? 6 : 7;
+    if (tiles256 < 37) {
+        // Fewer 256 x 256 tiles than half the CTA pairs (M sweep: M = 729 .. 1458 at the So400m shapes):
+        // 128 x 128 tiles on single CTAs give more of the 148 SMs work.
+        return 6;
     }
     // A tcgen05.mma of a CTA pair takes about 150 cycles whatever its N (measured for N = 128, 192,
     // 256), so the widest tile does the most work per instruction even where N = 1152 leaves the

@@ -55,8 +55,8 @@ def test_query_config_without_handle(lib):
     assert cfg.tile_n == 256 and cfg.grid in (148, 296 // 2)
     assert lib.sl8_query_config(None, L.SL8_OP_FC2_RESIDUAL, L.SL8_OUT_BF16, 46656, 1152, 4304, C.byref(cfg)) == 0
     assert cfg.tile_n == 256
-    assert lib.sl8_query_config(None, L.SL8_OP_FC1_GELU, L.SL8_OUT_BF16, 729, 4304, 1152, C.byref(cfg)) == 0
-    assert cfg.tile_n == 128                       # too few 256-wide tiles for 148 SMs
+    assert lib.sl8_query_config(None, L.SL8_OP_FC2_RESIDUAL, L.SL8_OUT_BF16, 729, 1152, 4304, C.byref(cfg)) == 0
+    assert cfg.tile_n == 128 and cfg.cta_group == 1       # too few 256-wide tiles for 148 SMs
     assert lib.sl8_query_config(None, 7, 0, 10, 16, 16, C.byref(cfg)) == L.SL8_ERR_INVALID_VALUE
 
 

@@ -146,6 +146,26 @@ def test_every_variant(engine, oracle, vid):
         assert err.value.code == L.SL8_ERR_UNSUPPORTED
 
 
+def test_fc1_fc2_chain_through_e4m3(engine, oracle):
+    """The MLP chain of the block: FC1 writes e4m3 straight into FC2's operand buffer (row pitch 4352, a
+    multiple of 128), FC2 adds bias and residual.  FC1's codes are checked against the oracle's, FC2 against
+    the oracle run on the very codes FC1 produced."""
+    M, D_MODEL, D_FF = 1000, 1152, 4304
+    p1 = synth.make_fc1(M, D_FF, D_MODEL, seed=31, device=DEV)
+    p2 = synth.make_fc2(M, D_MODEL, D_FF, seed=32, device=DEV)                 # weights, bias, residual of FC2
+    h_scale = 0.0125                                                           # static activation scale
+    H = torch.zeros((M, synth.pitch128(D_FF)), dtype=torch.uint8, device=DEV)[:, :D_FF]
+    engine.fc1_gelu(p1.A, p1.B, p1.bias, scale_a=dscalar(p1.scale_a), scale_b=dscalar(p1.scale_b), out=H,
+                    out_dtype=torch.uint8, out_scale=dscalar(h_scale))
+    D = engine.fc2_residual(H, p2.B, p2.bias, p2.residual, scale_a=dscalar(h_scale), scale_b=dscalar(p2.scale_b))
+    engine.device_status()
+    h_ref = oracle.fc1_gelu(p1.A.cpu().numpy(), p1.B.cpu().numpy(), p1.scale_a, p1.scale_b, bits(p1.bias),
+                            out_e4m3=True, out_scale=h_scale)
+    check_e4m3(H.cpu().numpy(), h_ref, "chain: FC1 e4m3 output")
+    d_ref = oracle.fc2_residual(H.cpu().numpy(), p2.B.cpu().numpy(), h_scale, p2.scale_b, bits(p2.bias), bits(p2.residual))
+    check_bf16(bits(D), d_ref, "chain: FC2 on FC1's codes")
+
+
 def test_multi_wave_determinism(engine, oracle):
     """More tiles than SMs (several rounds of the persistent loop and both TMEM buffers), twice: bit-equal runs."""
     p = synth.make_fc1(6000, 2304, 1152, seed=3, device=DEV)
