@@ -23,6 +23,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OBJ = PKG / "lib" / "obj"
 LIB = PKG / "lib" / "libsiglip_fp8.so"
+BENCH = PKG / "lib" / "siglip_bench"      # per-layer bench host speaking the reference harness's @@RESULT protocol
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH_FLAGS + ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hidden",
@@ -67,7 +68,7 @@ def compile_one(args: tuple[list[str], Path, bool]) -> str:
 
 def build(force: bool = False, verbose: bool = False) -> Path:
     """Compiles what is out of date and returns the path of the shared library."""
-    if LIB.exists() and not force and LIB.stat().st_mtime >= sources_mtime():
+    if LIB.exists() and BENCH.exists() and not force and min(LIB.stat().st_mtime, BENCH.stat().st_mtime) >= sources_mtime():
         return LIB
     OBJ.mkdir(parents=True, exist_ok=True)
     for stale in list(OBJ.glob("variant_*.o")) + list(OBJ.glob("variant_*.log")):
@@ -90,6 +91,11 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     res = subprocess.run(link, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"link failed: {' '.join(link)}\n{res.stdout}\n{res.stderr}")
+    bench = [exe, *ARCH_FLAGS, "-O3", "-std=c++17", "-lineinfo", str(CSRC / "sl8_bench.cu"), "-o", str(BENCH),
+             f"-L{LIB.parent}", "-lsiglip_fp8", "-Xlinker", "-rpath=$ORIGIN", "-cudart", "static"]
+    res = subprocess.run(bench, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"bench host build failed: {' '.join(bench)}\n{res.stdout}\n{res.stderr}")
     return LIB
 
 

@@ -160,7 +160,7 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, const Wa
     unsigned long long t0 = 0;
     for (uint32_t spins = 1;; ++spins) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((spins & 127u) == 0) {
+        if ((spins & 15u) == 0) {   // each poll may have been parked for up to 20 us
             if (*w.abort_flag) return false;
             const unsigned long long now = globaltimer_ns();
             if (t0 == 0) {
