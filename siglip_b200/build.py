@@ -30,6 +30,7 @@ NVCC_FLAGS = ARCH_FLAGS + ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPI
                            "-Xptxas", "-v"]
 if os.environ.get("SL8_DIAG"):          # measurement aids in the kernels (see SL8_DBG in sl8_kernel.cuh)
     NVCC_FLAGS.append("-DSL8_DIAG")
+NVCC_FLAGS += os.environ.get("SL8_NVCC_DEFINES", "").split()   # tuning macros, e.g. -DSL8_MMA_UNROLL=2
 
 
 def nvcc() -> str:

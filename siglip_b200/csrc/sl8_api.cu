@@ -150,7 +150,12 @@ int validate(sl8_handle_t h, const Problem& q) {
     if (q.M > 0x7FFFFF00ll) return fail(h, SL8_ERR_UNSUPPORTED, "M exceeds 2^31 rows");
     if (q.out_dtype != SL8_OUT_BF16 && q.out_dtype != SL8_OUT_E4M3)
         return fail(h, SL8_ERR_INVALID_VALUE, "unknown out_dtype");
-    if (q.flags & ~(unsigned)(SL8_FLAG_BIAS_F32 | SL8_FLAG_PE_F32_ADD | 0x1FF00u)) return fail(h, SL8_ERR_INVALID_VALUE, "unknown flag bits");
+#ifdef SL8_DIAG
+    constexpr unsigned kDiagBits = 0xFFFFFF00u;   // measurement builds only: skip-a-part switches
+#else
+    constexpr unsigned kDiagBits = 0u;
+#endif
+    if (q.flags & ~(unsigned)(SL8_FLAG_BIAS_F32 | SL8_FLAG_PE_F32_ADD | kDiagBits)) return fail(h, SL8_ERR_INVALID_VALUE, "unknown flag bits");
     if (q.N % 16 != 0) return fail(h, SL8_ERR_UNSUPPORTED, "N must be a multiple of 16");
     if (q.lda < q.K || q.ldb < q.K) return fail(h, SL8_ERR_INVALID_VALUE, "lda / ldb smaller than K");
     if (q.ldd < q.N) return fail(h, SL8_ERR_INVALID_VALUE, "ldd smaller than N");

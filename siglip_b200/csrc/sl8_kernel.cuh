@@ -52,7 +52,8 @@ enum : int { OUT_BF16 = 0, OUT_E4M3 = 1 };
 enum : unsigned { FLAG_BIAS_F32 = 1u, FLAG_PE_F32_ADD = 2u,
                   DBG_SKIP_SIDE = 0x100u, DBG_SKIP_GELU = 0x200u, DBG_SKIP_BIAS = 0x400u, DBG_SKIP_STORE = 0x800u,
                   DBG_SKIP_LOAD = 0x1000u, DBG_SKIP_EPILOGUE = 0x2000u, DBG_SKIP_MMA = 0x4000u,
-                  DBG_SKIP_A = 0x8000u, DBG_SKIP_B = 0x10000u };
+                  DBG_SKIP_A = 0x8000u, DBG_SKIP_B = 0x10000u,
+                  DBG_COARSE_TRACE = 0x80000000u };   // MMA thread records totals only (its inner timers cost ~35 cycles each)
 
 // status[0] codes: which role gave up.
 enum : uint32_t {
@@ -136,14 +137,18 @@ struct KernelTraits {
     static constexpr int COLS_PER_WARP = TN / (EPI_WARPS / 4);   // columns one epilogue warp covers
     static constexpr int REGIONS_PER_TILE = COLS_PER_WARP / REGION_COLS;
     static constexpr int CHUNKS_PER_REGION = REGION_COLS / 32;   // 32-column tcgen05.ld chunks per region
+    static constexpr int BAR_BYTES = 512;                        // pipeline barriers + two per staging box
     static constexpr int BIAS_BYTES = EPI_WARPS * COLS_PER_WARP * 4;   // fp32 bias of the current tile, one copy per warp
     static constexpr int THREADS = (3 + EPI_WARPS) * 32;         // producer, MMA, epilogue warps, side-data loader
-    static constexpr int BAR_BYTES = 512;                        // pipeline barriers + two per staging box
     static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STAGING_BYTES + BIAS_BYTES + BAR_BYTES;
     static_assert(STAGE_BYTES % 1024 == 0, "every operand tile must start on a swizzle-atom boundary");
     static_assert(COLS_PER_WARP % REGION_COLS == 0, "a warp stores whole staging regions");
     static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB a CTA may use");
 };
+
+#ifndef SL8_MMA_UNROLL
+#define SL8_MMA_UNROLL 2
+#endif
 
 struct WaitCtx {
     volatile uint32_t* abort_flag;  // shared memory, one per CTA
@@ -345,7 +350,9 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
     const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
     const int lane = threadIdx.x & 31;
-    const uint32_t cta_rank = (CG == 2) ? cluster_ctarank() : 0u;
+    // Rank inside the CTA pair.  Clusters are (2,1,1) on a one-dimensional grid, so the rank is the parity of
+    // blockIdx.x; taking it from there (not from %cluster_ctarank) lets the compiler see it as warp-uniform.
+    const uint32_t cta_rank = (CG == 2) ? (blockIdx.x & 1u) : 0u;
     const int cluster_id = blockIdx.x / CG;
     const int num_clusters = gridDim.x / CG;
 
@@ -452,49 +459,97 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         __syncwarp();
     } else if (warp == 1) {
         // ===== MMA issuer (leader CTA only) =====
+        // One thread.  Measured on B200: issuing one tcgen05.mma holds the thread for ~108 cycles and the MMA
+        // (M 256, N 256, K 32) itself takes 128, so whatever else this thread executes per k-block (~290 cycles
+        // for wait + commit + loop control when written naively) decides whether the tensor pipe idles.  Hence:
+        // the poll of the NEXT stage's barrier is issued before this stage's MMAs and read after them (the
+        // blocking wait runs only if that look-ahead failed), and k-blocks are taken several per loop iteration.
         if (lane == 0 && cta_rank == 0) {
             const uint32_t idesc = make_idesc_e4m3_f32(T::TILE_M_CTA * CG, TN);
-            // Descriptors differ between stages only in the 14-bit start-address field.
+            // Descriptors differ between stages, atoms and K steps only in the 14-bit start-address
+            // field: +2 there = 32 bytes = one K = 32 step inside the 128-byte row.
             const uint64_t adesc0 = make_kmajor_sw128_desc(base);
             const uint64_t bdesc0 = make_kmajor_sw128_desc(base + T::A_BYTES);
+            constexpr uint32_t STAGE_DESC = T::STAGE_BYTES >> 4;
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            const bool prof = p.prof != nullptr;
+            const bool prof_any = p.prof != nullptr;
+#ifdef SL8_DIAG
+            const bool prof = prof_any && !(p.flags & DBG_COARSE_TRACE);
+#else
+            const bool prof = prof_any;
+#endif
             long long t_full = 0, t_tmem = 0, n_tiles = 0, t_mma = 0, t_commit = 0;
             const long long t_begin = clock64();
+            uint32_t ready = 0;      // look-ahead: the barrier of `stage` was already seen complete
+
+            // All MMAs of one full k-block held in `st`; `fresh` = this k-block starts a tile (overwrite D).
+            auto issue_full = [&](uint32_t d_tmem, int st, bool fresh) {
+                const uint64_t adesc = adesc0 + static_cast<uint32_t>(st) * STAGE_DESC;
+                const uint64_t bdesc = bdesc0 + static_cast<uint32_t>(st) * STAGE_DESC;
+#pragma unroll
+                for (int j = 0; j < 4 * T::KATOMS; j++) {
+                    const uint32_t o = (j >> 2) * (T::A_ATOM_BYTES >> 4) + 2 * (j & 3);
+                    const uint32_t ob = (j >> 2) * (T::B_ATOM_BYTES >> 4) + 2 * (j & 3);
+                    mma_f8<CG>(d_tmem, adesc + o, bdesc + ob, idesc, (j == 0 && fresh) ? 0u : 1u);
+                }
+            };
+            auto release_stage = [&](int st) {
+                if constexpr (CG == 2) mma_commit_pair(empty_bar0 + 8 * st, 0x3);
+                else mma_commit(empty_bar0 + 8 * st);
+            };
+
             for (int tile = cluster_id; ok && tile < p.num_tiles; tile += num_clusters) {
                 wc.tile = tile;
                 long long t0 = prof ? clock64() : 0;
                 ok = wait_bar(tempty_bar0 + 8 * acc, acc_phase ^ 1u, wc, ST_MMA_TMEM_EMPTY_WAIT, acc);
-                if (prof) { t_tmem += clock64() - t0; n_tiles++; }
+                if (prof) t_tmem += clock64() - t0;
+                n_tiles++;
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * T::ACC_STRIDE;
-                for (int kb = 0; kb < p.k_blocks; kb++) {
+                int kb = 0;
+                const int k_full = p.k_blocks - 1;           // k-blocks that hold all their MMAs
+                if (!prof && !SL8_DBG(p.flags, DBG_SKIP_MMA)) {
+                    constexpr int U = SL8_MMA_UNROLL;     // full k-blocks per loop iteration
+                    for (; ok && kb + U <= k_full; kb += U) {
+#pragma unroll
+                        for (int u = 0; u < U; u++) {
+                            if (!ready) ok = wait_bar(full_bar0 + 8 * stage, phase, wc, ST_MMA_FULL_WAIT, stage);
+                            if (!ok) break;
+                            const int s1 = (stage + 1 == STAGES) ? 0 : stage + 1;
+                            const uint32_t ph1 = (s1 == 0) ? (phase ^ 1u) : phase;
+                            const uint32_t r1 = mbar_test_wait(full_bar0 + 8 * s1, ph1);
+                            tc_fence_after();
+                            issue_full(d_tmem, stage, u == 0 && kb == 0);
+                            release_stage(stage);
+                            stage = s1;
+                            phase = ph1;
+                            ready = r1;
+                        }
+                    }
+                    if (!ok) break;
+                }
+                for (; kb < p.k_blocks; kb++) {
                     if (prof) t0 = clock64();
-                    ok = wait_bar(full_bar0 + 8 * stage, phase, wc, ST_MMA_FULL_WAIT, stage);
+                    if (!ready) ok = wait_bar(full_bar0 + 8 * stage, phase, wc, ST_MMA_FULL_WAIT, stage);
                     if (prof) t_full += clock64() - t0;
                     if (!ok) break;
+                    const int s1 = (stage + 1 == STAGES) ? 0 : stage + 1;
+                    const uint32_t ph1 = (s1 == 0) ? (phase ^ 1u) : phase;
+                    ready = mbar_test_wait(full_bar0 + 8 * s1, ph1);
                     tc_fence_after();
-                    // Descriptors differ between stages, atoms and K steps only in the 14-bit start-address
-                    // field: +2 there = 32 bytes = one K = 32 step inside the 128-byte row.
-                    const uint32_t soff = static_cast<uint32_t>(stage) * (T::STAGE_BYTES >> 4);
-                    const uint64_t adesc = adesc0 + soff;
-                    const uint64_t bdesc = bdesc0 + soff;
                     long long t1 = prof ? clock64() : 0;
                     if (SL8_DBG(p.flags, DBG_SKIP_MMA)) {
                         // measurement aid: stages are released at once, the loads run at their own pace
-                    } else if (kb < p.k_blocks - 1) {
-#pragma unroll
-                        for (int j = 0; j < 4 * T::KATOMS; j++) {
-                            const uint32_t o = (j >> 2) * (T::A_ATOM_BYTES >> 4) + 2 * (j & 3);
-                            const uint32_t ob = (j >> 2) * (T::B_ATOM_BYTES >> 4) + 2 * (j & 3);
-                            mma_f8<CG>(d_tmem, adesc + o, bdesc + ob, idesc, (j == 0 && kb == 0) ? 0u : 1u);
-                        }
+                    } else if (kb < k_full) {
+                        issue_full(d_tmem, stage, kb == 0);
                     } else {
+                        const uint64_t adesc = adesc0 + static_cast<uint32_t>(stage) * STAGE_DESC;
+                        const uint64_t bdesc = bdesc0 + static_cast<uint32_t>(stage) * STAGE_DESC;
                         for (int j = 0; j < p.last_kblock_mmas; j++) {
                             const uint32_t o = (j >> 2) * (T::A_ATOM_BYTES >> 4) + 2 * (j & 3);
                             const uint32_t ob = (j >> 2) * (T::B_ATOM_BYTES >> 4) + 2 * (j & 3);
@@ -502,10 +557,10 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         }
                     }
                     if (prof) { const long long t2 = clock64(); t_mma += t2 - t1; t1 = t2; }
-                    if constexpr (CG == 2) mma_commit_pair(empty_bar0 + 8 * stage, 0x3);
-                    else mma_commit(empty_bar0 + 8 * stage);
+                    release_stage(stage);
                     if (prof) t_commit += clock64() - t1;
-                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                    stage = s1;
+                    phase = ph1;
                 }
                 if (!ok) break;
                 if constexpr (CG == 2) mma_commit_pair(tfull_bar0 + 8 * acc, 0x3);
@@ -513,7 +568,7 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 acc ^= 1;
                 if (acc == 0) acc_phase ^= 1u;
             }
-            if (prof) {
+            if (prof_any) {
                 long long* slot = p.prof + static_cast<size_t>(blockIdx.x) * PROF_SLOTS;
                 slot[PROF_MMA_WAIT_FULL] = t_full;
                 slot[PROF_MMA_WAIT_TMEM] = t_tmem;
@@ -561,14 +616,14 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 __syncwarp();
             }
         }
+        bool ok = true;
         uint32_t seq = 0;                          // regions processed so far by this warp
         int acc = 0;
         uint32_t acc_phase = 0;
-        bool ok = true;
         const bool prof = p.prof != nullptr && ew == 0;
         long long t_acc = 0, t_store = 0, t_ld = 0, t_math = 0, t_issue = 0, t_refill = 0;
         const long long t_begin = clock64();
-        for (int tile = cluster_id; tile < p.num_tiles; tile += num_clusters) {
+        for (int tile = cluster_id; ok && tile < p.num_tiles; tile += num_clusters) {
             wc.tile = tile;
             const int tm = tile / p.tiles_n;
             const int tn = tile - tm * p.tiles_n;
@@ -639,8 +694,8 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                 released = true;
                             }
                             if (prof) t0 = clock64();
-                            const float* bias32 = bias_w + (c - col_begin);
                             const int piece0 = ch * 2 * T::OUT_BYTES;            // 32 columns = 2 (e4m3) or 4 (bf16) pieces
+                            const float* bias32 = bias_w + (c - col_begin);
                             epilogue_16<OP, OUT, 0>(v, e, bias32, region, piece0);
                             if (n0 + c + 16 < p.N) epilogue_16<OP, OUT, 1>(v, e, bias32 + 16, region, piece0 + T::OUT_BYTES);
                             if (prof) t_math += clock64() - t0;

@@ -75,6 +75,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// One poll that never parks the thread: safe on a barrier that may never complete (a look-ahead).
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+
 // Arrive on a barrier of this CTA and add `bytes` to the transaction count it waits for.
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
@@ -130,6 +143,14 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* map, 
         " [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
         "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
         : "memory");
+}
+
+// Hint: bring one box of a tiled tensor into L2 (no shared-memory destination, no barrier).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const void* map, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(
+                     reinterpret_cast<uint64_t>(map)),
+                 "r"(x), "r"(y)
+                 : "memory");
 }
 
 // 2-D tiled store shared -> global (clipped at the tensor's edges by the hardware).
