@@ -53,7 +53,7 @@ enum : unsigned { FLAG_BIAS_F32 = 1u, FLAG_PE_F32_ADD = 2u,
                   DBG_SKIP_SIDE = 0x100u, DBG_SKIP_GELU = 0x200u, DBG_SKIP_BIAS = 0x400u, DBG_SKIP_STORE = 0x800u,
                   DBG_SKIP_LOAD = 0x1000u, DBG_SKIP_EPILOGUE = 0x2000u, DBG_SKIP_MMA = 0x4000u,
                   DBG_SKIP_A = 0x8000u, DBG_SKIP_B = 0x10000u,
-                  DBG_COARSE_TRACE = 0x80000000u };   // MMA thread records totals only (its inner timers cost ~35 cycles each)
+                  DBG_COARSE_TRACE = 0x80000000u };   // record per-role totals only (the inner timers cost ~35 cycles each)
 
 // status[0] codes: which role gave up.
 enum : uint32_t {
@@ -620,7 +620,8 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         uint32_t seq = 0;                          // regions processed so far by this warp
         int acc = 0;
         uint32_t acc_phase = 0;
-        const bool prof = p.prof != nullptr && ew == 0;
+        const bool prof_total = p.prof != nullptr && ew == 0;
+        const bool prof = prof_total && !SL8_DBG(p.flags, DBG_COARSE_TRACE);   // inner timers cost ~35 cycles each
         long long t_acc = 0, t_store = 0, t_ld = 0, t_math = 0, t_issue = 0, t_refill = 0;
         const long long t_begin = clock64();
         for (int tile = cluster_id; ok && tile < p.num_tiles; tile += num_clusters) {
@@ -745,7 +746,7 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
         if (lane == 0) tma_store_wait_all<0>();
         __syncwarp();
-        if (prof && lane == 0) {
+        if (prof_total && lane == 0) {
             long long* slot = p.prof + static_cast<size_t>(blockIdx.x) * PROF_SLOTS;
             slot[PROF_EPI_WAIT_ACC] = t_acc;
             slot[PROF_EPI_WAIT_STORE] = t_store;
