@@ -146,10 +146,6 @@ struct KernelTraits {
     static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB a CTA may use");
 };
 
-#ifndef SL8_MMA_UNROLL
-#define SL8_MMA_UNROLL 2
-#endif
-
 struct WaitCtx {
     volatile uint32_t* abort_flag;  // shared memory, one per CTA
     uint32_t* status;
@@ -514,22 +510,43 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 int kb = 0;
                 const int k_full = p.k_blocks - 1;           // k-blocks that hold all their MMAs
                 if (!prof && !SL8_DBG(p.flags, DBG_SKIP_MMA)) {
-                    constexpr int U = SL8_MMA_UNROLL;     // full k-blocks per loop iteration
-                    for (; ok && kb + U <= k_full; kb += U) {
+                    // One k-block: wait (only if the look-ahead failed), look ahead, MMAs, release the stage.
+                    // n < 4 * KATOMS only in the K tail.
+                    auto step = [&](bool fresh, int n) -> bool {
+                        if (!ready && !wait_bar(full_bar0 + 8 * stage, phase, wc, ST_MMA_FULL_WAIT, stage)) return false;
+                        const int s1 = (stage + 1 == STAGES) ? 0 : stage + 1;
+                        const uint32_t ph1 = (s1 == 0) ? (phase ^ 1u) : phase;
+                        const uint32_t r1 = mbar_test_wait(full_bar0 + 8 * s1, ph1);
+                        tc_fence_after();
+                        if (n == 4 * T::KATOMS) {
+                            issue_full(d_tmem, stage, fresh);
+                        } else {
+                            const uint64_t adesc = adesc0 + static_cast<uint32_t>(stage) * STAGE_DESC;
+                            const uint64_t bdesc = bdesc0 + static_cast<uint32_t>(stage) * STAGE_DESC;
 #pragma unroll
-                        for (int u = 0; u < U; u++) {
-                            if (!ready) ok = wait_bar(full_bar0 + 8 * stage, phase, wc, ST_MMA_FULL_WAIT, stage);
-                            if (!ok) break;
-                            const int s1 = (stage + 1 == STAGES) ? 0 : stage + 1;
-                            const uint32_t ph1 = (s1 == 0) ? (phase ^ 1u) : phase;
-                            const uint32_t r1 = mbar_test_wait(full_bar0 + 8 * s1, ph1);
-                            tc_fence_after();
-                            issue_full(d_tmem, stage, u == 0 && kb == 0);
-                            release_stage(stage);
-                            stage = s1;
-                            phase = ph1;
-                            ready = r1;
+                            for (int j = 0; j < 4 * T::KATOMS - 1; j++) {
+                                const uint32_t o = (j >> 2) * (T::A_ATOM_BYTES >> 4) + 2 * (j & 3);
+                                const uint32_t ob = (j >> 2) * (T::B_ATOM_BYTES >> 4) + 2 * (j & 3);
+                                if (j < n) mma_f8<CG>(d_tmem, adesc + o, bdesc + ob, idesc, (j == 0 && fresh) ? 0u : 1u);
+                            }
                         }
+                        release_stage(stage);
+                        stage = s1;
+                        phase = ph1;
+                        ready = r1;
+                        return true;
+                    };
+                    for (; ok && kb + 2 <= k_full; kb += 2) {      // two k-blocks per loop iteration
+                        ok = step(kb == 0, 4 * T::KATOMS);
+                        if (ok) ok = step(false, 4 * T::KATOMS);
+                    }
+                    if (ok && kb < k_full) {
+                        ok = step(kb == 0, 4 * T::KATOMS);
+                        kb++;
+                    }
+                    if (ok) {
+                        ok = step(kb == 0, p.last_kblock_mmas);
+                        kb++;
                     }
                     if (!ok) break;
                 }
