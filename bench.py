@@ -38,7 +38,7 @@ UNIT = "TFLOP/s"
 # DRAM bytes per GEMM row of the dominant kernel, from one `ncu --set full` capture per configuration on a
 # smaller case (profiles/*_ncu.md: dram__bytes_read.sum + dram__bytes_write.sum divided by the rows of the
 # captured launch).  Traffic grows in proportion to the rows, so a full launch is this figure times M.
-NCU_DRAM_BYTES_PER_ROW = {"C2": 321.59e6 / 37908, "C3": 327.73e6 / 37908, "C4": 169.39e6 / 75816}
+NCU_DRAM_BYTES_PER_ROW = {"C2": 320.32e6 / 37908, "C3": 325.66e6 / 37908, "C4": 167.73e6 / 75816}
 
 
 # ----------------------------------------------------------------------------- peaks
@@ -325,6 +325,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="C2", choices=["C1", "C2", "C3", "C4", "C5"])
     ap.add_argument("--layers", action="store_true", help="also time C1, C3 and C4 and add them under 'layers'")
+    ap.add_argument("--layer-names", default="C1,C2,C3,C4", help="which configurations --layers covers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--variant", type=int, default=-1, help="force a kernel variant (sweeps)")
@@ -462,7 +463,7 @@ def main() -> None:
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
                                     "seconds": secs}
         if args.layers:
-            line["layers"] = layer_table(eng, dev, max(20, min(args.steps, 100)), peaks)
+            line["layers"] = layer_table(eng, dev, max(20, min(args.steps, 100)), peaks, tuple(args.layer_names.split(",")))
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
