@@ -80,7 +80,9 @@ enum {
     SL8_FLAG_BIAS_F32    = 1,
     /* patch-embed: add the table in fp32 and round once, instead of the reference's
      * bf16-domain add of bf16(acc) and the table (patch_embed.cu:44-58). */
-    SL8_FLAG_PE_F32_ADD  = 2
+    SL8_FLAG_PE_F32_ADD  = 2,
+    /* FC1 entry points: no activation, D = acc * scale + bias (what sl8_linear_bias_fp8 sets). */
+    SL8_FLAG_NO_ACTIVATION = 4
 };
 
 /* Which kernel variant the dispatch table picks for a problem. */
@@ -161,6 +163,19 @@ int sl8_fc1_gelu_fp8(sl8_handle_t h,
                      void* D, int64_t ldd, int out_dtype, const float* out_scale,
                      int64_t M, int N, int K,
                      unsigned flags, sl8_stream_t stream);
+
+/* GEMM + bias with no activation: the block's Q, K, V projections (the reference lists them as the next
+ * GEMMs of the block, docs/architecture.md:76-90, and has no kernel for them; the output projection, bias +
+ * residual, is sl8_fc2_residual_fp8).  Same kernels, arguments and output types as sl8_fc1_gelu_fp8, of which
+ * this is the SL8_FLAG_NO_ACTIVATION form: D = bf16(acc * scale_a * scale_b + bias) or its e4m3 quantisation. */
+int sl8_linear_bias_fp8(sl8_handle_t h,
+                        const void* A, int64_t lda,
+                        const void* B, int64_t ldb,
+                        const float* scale_a, const float* scale_b,
+                        const void* bias,
+                        void* D, int64_t ldd, int out_dtype, const float* out_scale,
+                        int64_t M, int N, int K,
+                        unsigned flags, sl8_stream_t stream);
 
 /* FC2 GEMM + bias + residual.  Replaces persistent_gemm<BIAS_RESIDUAL>
  * (fc2.cu:162,178; epilogue fc2.cu:19-54): D = bf16((acc + bias) + float(residual)). */

@@ -304,7 +304,7 @@ SL8O_API int sl8o_fc1_gelu(const uint8_t* A, int64_t lda, const uint8_t* B, int6
             const int64_t m = r0 + i;
             for (int n = 0; n < N; n++) {
                 const float x = acc[i * N + n] * s + bias_at(bias, n, flags);
-                const float g = sl8o_gelu_tanh(x);                                  /* fc1_gelu.cu:16-19 */
+                const float g = (flags & 4u) ? x : sl8o_gelu_tanh(x);   /* fc1_gelu.cu:16-19; flag 4: no activation */
                 if (out_dtype == 0) ((uint16_t*)D)[m * ldd + n] = sl8o_f32_to_bf16(g);
                 else ((uint8_t*)D)[m * ldd + n] = sl8o_f32_to_e4m3(g * inv_out);
             }

@@ -16,6 +16,7 @@
 
 #include "../../include/siglip_fp8.h"
 #include "sl8_variants.h"
+#include "sl8_dispatch_table.h"
 
 #define SL8_API extern "C" __attribute__((visibility("default")))
 
@@ -107,11 +108,22 @@ struct DeviceGuard {
 };
 
 // ---- dispatch -------------------------------------------------------------------------
-// Chosen from the sweep recorded in profiles/ (one line per rule; the first match wins).
+// The table is generated from a sweep on B200 (python -m siglip_b200.sweep); shapes it does not hold fall back
+// to rules (one line per rule; the first match wins).
 int pick_variant(int op, int out_dtype, long long M, int N, int K) {
     (void)out_dtype;
-    (void)K;
-    (void)N;
+    // A (layer, N, K) the committed sweep covers: the row with the largest m_min <= M decides.
+    int swept = -1;
+    long long swept_m = -1;
+    for (int i = 0; i < kSl8DispatchRows; i++) {
+        const Sl8DispatchRow& r = kSl8DispatchTable[i];
+        if (r.op == op && r.n == N && r.k == K && r.m_min <= M && r.m_min > swept_m) {
+            swept = r.variant;
+            swept_m = r.m_min;
+        }
+    }
+    if (swept >= 0 && swept < SL8_NUM_VARIANTS) return swept;
+    // Any other shape: the rules the sweeps suggest.
     const long long tiles256 = ((M + 255) / 256) * ((N + 255) / 256);
     if (tiles256 < 37) {
         // Fewer 256 x 256 tiles than half the CTA pairs (M sweep: M = 729 .. 1458 at the So400m shapes):
@@ -155,7 +167,10 @@ int validate(sl8_handle_t h, const Problem& q) {
 #else
     constexpr unsigned kDiagBits = 0u;
 #endif
-    if (q.flags & ~(unsigned)(SL8_FLAG_BIAS_F32 | SL8_FLAG_PE_F32_ADD | kDiagBits)) return fail(h, SL8_ERR_INVALID_VALUE, "unknown flag bits");
+    if (q.flags & ~(unsigned)(SL8_FLAG_BIAS_F32 | SL8_FLAG_PE_F32_ADD | SL8_FLAG_NO_ACTIVATION | kDiagBits))
+        return fail(h, SL8_ERR_INVALID_VALUE, "unknown flag bits");
+    if ((q.flags & SL8_FLAG_NO_ACTIVATION) && q.op != SL8_OP_FC1_GELU)
+        return fail(h, SL8_ERR_INVALID_VALUE, "SL8_FLAG_NO_ACTIVATION belongs to the FC1 entry points");
     if (q.N % 16 != 0) return fail(h, SL8_ERR_UNSUPPORTED, "N must be a multiple of 16");
     if (q.lda < q.K || q.ldb < q.K) return fail(h, SL8_ERR_INVALID_VALUE, "lda / ldb smaller than K");
     if (q.ldd < q.N) return fail(h, SL8_ERR_INVALID_VALUE, "ldd smaller than N");
@@ -449,6 +464,14 @@ SL8_API int sl8_fc1_gelu_fp8(sl8_handle_t h, const void* A, int64_t lda, const v
     q.bias = bias;
     q.D = D; q.ldd = ldd; q.M = M; q.N = N; q.K = K; q.flags = flags;
     return run(h, q, static_cast<cudaStream_t>(stream));
+}
+
+SL8_API int sl8_linear_bias_fp8(sl8_handle_t h, const void* A, int64_t lda, const void* B, int64_t ldb,
+                                const float* scale_a, const float* scale_b, const void* bias, void* D, int64_t ldd,
+                                int out_dtype, const float* out_scale, int64_t M, int N, int K, unsigned flags,
+                                sl8_stream_t stream) {
+    return sl8_fc1_gelu_fp8(h, A, lda, B, ldb, scale_a, scale_b, bias, D, ldd, out_dtype, out_scale, M, N, K,
+                            flags | SL8_FLAG_NO_ACTIVATION, stream);
 }
 
 SL8_API int sl8_fc2_residual_fp8(sl8_handle_t h, const void* A, int64_t lda, const void* B, int64_t ldb,

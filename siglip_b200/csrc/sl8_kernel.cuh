@@ -49,7 +49,7 @@ enum : int { OUT_BF16 = 0, OUT_E4M3 = 1 };
 #define SL8_DBG(flags, bit) false
 #endif
 
-enum : unsigned { FLAG_BIAS_F32 = 1u, FLAG_PE_F32_ADD = 2u,
+enum : unsigned { FLAG_BIAS_F32 = 1u, FLAG_PE_F32_ADD = 2u, FLAG_NO_ACTIVATION = 4u,
                   DBG_SKIP_SIDE = 0x100u, DBG_SKIP_GELU = 0x200u, DBG_SKIP_BIAS = 0x400u, DBG_SKIP_STORE = 0x800u,
                   DBG_SKIP_LOAD = 0x1000u, DBG_SKIP_EPILOGUE = 0x2000u, DBG_SKIP_MMA = 0x4000u,
                   DBG_SKIP_A = 0x8000u, DBG_SKIP_B = 0x10000u,
@@ -259,7 +259,7 @@ __device__ __forceinline__ void epilogue_16(const float (&v)[32], const EpiCtx& 
             g[2 * i + 0] = fma_f32x2(pack_f32x2(v[16 * H + 4 * i + 0], v[16 * H + 4 * i + 1]), scale2, pack_f32x2(b.x, b.y));
             g[2 * i + 1] = fma_f32x2(pack_f32x2(v[16 * H + 4 * i + 2], v[16 * H + 4 * i + 3]), scale2, pack_f32x2(b.z, b.w));
         }
-        if (!SL8_DBG(e.flags, DBG_SKIP_GELU)) {
+        if (!(e.flags & FLAG_NO_ACTIVATION) && !SL8_DBG(e.flags, DBG_SKIP_GELU)) {   // warp-uniform
 #pragma unroll
             for (int i = 0; i < 8; i++) g[i] = gelu_tanh_x2(g[i]);
         }

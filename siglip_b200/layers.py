@@ -134,6 +134,22 @@ class Engine:
             int(flags), self._stream(stream)))
         return D
 
+    def linear_bias(self, A, B, bias, *, scale_a=None, scale_b=None, out_dtype=torch.bfloat16, out_scale=None,
+                    out=None, flags: int = 0, stream=None) -> torch.Tensor:
+        """D = cast((sa*sb*A.B^T + bias) / out_scale): the Q / K / V projections (no activation)."""
+        M, N, K = self._operands(A, B)
+        if bias is not None and bias.dtype == torch.float32:
+            flags |= _l.SL8_FLAG_BIAS_F32
+        elif bias is not None and bias.dtype != torch.bfloat16:
+            raise TypeError("bias must be bf16 or fp32")
+        e4 = out_dtype in (torch.float8_e4m3fn, torch.uint8)
+        D = self._new_out(M, N, out_dtype, A.device) if out is None else out
+        self._check(self._lib.sl8_linear_bias_fp8(
+            self._h, A.data_ptr(), A.stride(0), B.data_ptr(), B.stride(0), _ptr(scale_a), _ptr(scale_b), _ptr(bias),
+            D.data_ptr(), D.stride(0), _l.SL8_OUT_E4M3 if e4 else _l.SL8_OUT_BF16, _ptr(out_scale), M, N, K,
+            int(flags), self._stream(stream)))
+        return D
+
     def fc2_residual(self, A, B, bias, residual, *, scale_a=None, scale_b=None, out=None, flags: int = 0,
                      stream=None) -> torch.Tensor:
         """D = bf16((sa*sb*A.B^T + bias) + residual); residual bf16 [M, N]."""

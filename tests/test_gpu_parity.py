@@ -99,6 +99,33 @@ def test_fc1_e4m3_output(engine, oracle, M, N, K):
     run_fc1(engine, oracle, M, N, K, seed=11, e4m3=True)
 
 
+@pytest.mark.parametrize("M,N,K,e4m3", [(729, 1152, 1152, False), (1000, 3456, 1152, False), (257, 1152, 1152, True)])
+def test_linear_bias_projection(engine, oracle, M, N, K, e4m3):
+    """The Q / K / V projections (N = 1152, or the three fused: 3456): GEMM + bias, no activation, against the
+    oracle's FC1 path with the activation switched off (flag 4)."""
+    p = synth.make_fc1(M, N, K, seed=21 + N, device=DEV)
+    kw = dict(scale_a=dscalar(p.scale_a), scale_b=dscalar(p.scale_b))
+    A, B = p.A.cpu().numpy(), p.B.cpu().numpy()
+    if e4m3:
+        D = engine.linear_bias(p.A, p.B, p.bias, out_dtype=torch.uint8, out_scale=dscalar(0.02), **kw)
+        engine.device_status()
+        ref = oracle.fc1_gelu(A, B, p.scale_a, p.scale_b, bits(p.bias), out_e4m3=True, out_scale=0.02, flags=4)
+        return check_e4m3(D.cpu().numpy(), ref, f"linear-e4m3 {M}x{N}x{K}")
+    D = engine.linear_bias(p.A, p.B, p.bias, **kw)
+    engine.device_status()
+    ref = oracle.fc1_gelu(A, B, p.scale_a, p.scale_b, bits(p.bias), flags=4)
+    check_bf16(bits(D), ref, f"linear {M}x{N}x{K}")
+    # and it is not the GELU layer
+    G = engine.fc1_gelu(p.A, p.B, p.bias, **kw)
+    assert not torch.equal(G, D)
+
+
+def test_no_activation_flag_is_refused_outside_fc1(engine):
+    p = synth.make_fc2(256, 256, 256, seed=3, device=DEV)
+    with pytest.raises(Exception):
+        engine.fc2_residual(p.A, p.B, p.bias, p.residual, flags=4)
+
+
 def test_fc1_fp32_bias(engine, oracle):
     run_fc1(engine, oracle, 300, 464, 588, seed=5, flags_f32_bias=True)
 

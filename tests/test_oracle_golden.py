@@ -126,3 +126,13 @@ def test_bf16_add_single_rounding(oracle):
     assert f.sl8o_bf16_add(one, 0x3B81) == 0x3F81          # just above the tie
     assert f.sl8o_bf16_add(0x44D8, 0x4080) == 0x44D8       # 1728 + 4 = 1732 -> tie between 1728 and 1736: even
     assert bf16_bits_to_f32(np.array([f.sl8o_bf16_add(0x44D8, 0x4100)], dtype=np.uint16))[0] == 1736.0
+
+
+def test_linear_bias_is_fc1_without_the_activation(oracle):
+    """Flag 4 of the FC1 oracle: acc * scale + bias, rounded once; closed form on the reference's constant operands
+    (acc = 2.25 K on even columns, 1.5 K on odd ones: patch_embed.cu:121-145)."""
+    M, N, K = 64, 128, 256
+    A, B, bias = ref_operands(M, N, K)
+    D = oracle.fc1_gelu(A, B, 1.0, 1.0, bias, flags=1 | 4)
+    want = acc_closed_form(N, K) + bias
+    assert np.array_equal(D, np.broadcast_to(f32_to_bf16_bits(want.astype(np.float32)), (M, N)))
