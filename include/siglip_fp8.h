@@ -189,6 +189,31 @@ int sl8_fc2_residual_fp8(sl8_handle_t h,
                          int64_t M, int N, int K,
                          unsigned flags, sl8_stream_t stream);
 
+/* ---- producer-side steps: what feeds A ---------------------------------------------------
+ * No counterpart in the reference, which starts at the GEMM operands (its docs describe the patch embedding as
+ * "Conv2d as GEMM", docs/architecture.md:11-12, and leave the unfold and the quantisation to the caller). */
+enum { SL8_DT_F32 = 0, SL8_DT_BF16 = 1 };
+
+/* Patch unfold fused with the per-tensor quantisation: pixels [images, channels, height, width] (contiguous, fp32
+ * or bf16) -> A [images * gh * gw, channels * patch * patch] e4m3 with row pitch lda, gh = height / patch,
+ * gw = width / patch (pixels past gh * patch, gw * patch are not used).  Row (img * gh + gy) * gw + gx, column
+ * c * patch^2 + py * patch + px -- the flattening of a Conv2d weight [N, C, patch, patch] -- holds
+ * e4m3_sat_rne(pixel * (1 / *scale)); scale is a device pointer to the activation scale the GEMM is given as scale_a
+ * (NULL = 1).  The pad columns up to lda are written as zeros when lda - K < 128. */
+int sl8_patchify_quantize_e4m3(sl8_handle_t h, const void* pixels, int pixel_dtype, int images, int channels,
+                               int height, int width, int patch, const float* scale,
+                               void* A, int64_t lda, sl8_stream_t stream);
+
+/* Dynamic per-tensor scale of an activation x [rows, cols] (fp32 or bf16, leading dimension ld elements):
+ * *amax = max |x| and, if scale is not NULL, *scale = amax / 448 (1 for an all-zero tensor).  Device pointers. */
+int sl8_amax_scale(sl8_handle_t h, const void* x, int dtype, int64_t rows, int cols, int64_t ld,
+                   float* amax, float* scale, sl8_stream_t stream);
+
+/* out[r, c] = e4m3_sat_rne(x[r, c] * (1 / *scale)): the quantisation FC1 fuses when it is given a static out_scale,
+ * as a separate pass for a scale that sl8_amax_scale has just produced. */
+int sl8_quantize_e4m3(sl8_handle_t h, const void* x, int dtype, int64_t rows, int cols, int64_t ld,
+                      const float* scale, void* out, int64_t ld_out, sl8_stream_t stream);
+
 /* ---- the same three layers with HOST operands ------------------------------------------
  * What each reference main() does around its launch (upload operands, launch, download
  * all of C: patch_embed.cu:111-154,249-252), as one call: rows are cut into slabs that

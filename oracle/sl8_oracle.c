@@ -345,3 +345,44 @@ SL8O_API void sl8o_combine_bias_pos(const float* bias, const float* pos, int per
         for (int c = 0; c < N; c++)
             table[(int64_t)r * N + c] = sl8o_f32_to_bf16(bias[c] + pos[(int64_t)r * N + c]);
 }
+
+/* ---- producer-side steps (test infrastructure like the rest of this file) -------------------------------
+ * Patch unfold + quantisation: the reference describes the patch embedding as "Conv2d as GEMM"
+ * (docs/architecture.md:11-12) and feeds its GEMM ready-made rows; the row/column order below is the
+ * flattening of a Conv2d weight [N, C, P, P] applied to non-overlapping patches in raster order. */
+SL8O_API int sl8o_patchify_quantize(const float* pixels, int images, int C, int H, int W, int P, float scale,
+                                    uint8_t* A, int64_t lda, int row_bytes) {
+    const int gh = H / P, gw = W / P, K = C * P * P;
+    const float inv = 1.0f / scale;
+    if (lda < K || row_bytes < K || row_bytes > lda) return -1;
+    for (int img = 0; img < images; img++)
+        for (int gy = 0; gy < gh; gy++)
+            for (int gx = 0; gx < gw; gx++) {
+                uint8_t* row = A + (((int64_t)img * gh + gy) * gw + gx) * lda;
+                for (int c = 0; c < C; c++)
+                    for (int py = 0; py < P; py++)
+                        for (int px = 0; px < P; px++) {
+                            const float v = pixels[(((int64_t)img * C + c) * H + (gy * P + py)) * W + gx * P + px];
+                            row[c * P * P + py * P + px] = sl8o_f32_to_e4m3(v * inv);
+                        }
+                for (int k = K; k < row_bytes; k++) row[k] = 0;
+            }
+    return 0;
+}
+
+SL8O_API float sl8o_amax(const float* x, int64_t rows, int cols, int64_t ld) {
+    float m = 0.0f;
+    for (int64_t r = 0; r < rows; r++)
+        for (int c = 0; c < cols; c++) {
+            const float a = fabsf(x[r * ld + c]);
+            if (a > m) m = a;
+        }
+    return m;
+}
+
+SL8O_API int sl8o_quantize_rows_e4m3(const float* x, int64_t rows, int cols, int64_t ld, float scale, uint8_t* out, int64_t ld_out) {
+    const float inv = 1.0f / scale;
+    for (int64_t r = 0; r < rows; r++)
+        for (int c = 0; c < cols; c++) out[r * ld_out + c] = sl8o_f32_to_e4m3(x[r * ld + c] * inv);
+    return 0;
+}

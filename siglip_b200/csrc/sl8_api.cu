@@ -774,3 +774,179 @@ SL8_API int sl8_extend_periodic_table(sl8_handle_t h, const void* table_in, int6
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? SL8_OK : fail_cuda(h, e, "table kernel launch");
 }
+
+// =========================================================================== producer-side steps
+// What feeds A: pixels -> patch rows (the Conv2d of the patch embedding written as a GEMM operand,
+// docs/architecture.md:11-12 of the reference, which stops at the GEMM) with the per-tensor quantisation to
+// e4m3 fused in, and the dynamic quantisation of a bf16 / fp32 activation (abs-max -> scale -> e4m3 codes)
+// for a caller that has no static scale between FC1 and FC2.  Byte work bounded by HBM.
+
+namespace {
+
+__device__ __forceinline__ float prep_load(const float* p) { return __ldg(p); }
+__device__ __forceinline__ float prep_load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ uint8_t prep_e4m3(float v) { return static_cast<uint8_t>(sl8::pack_e4m3x2(v, 0.0f) & 0xFFu); }
+
+// One block per (image, patch row): the C * P image rows of that strip are read with coalesced loads, quantised,
+// placed in shared memory at the position they have in the strip's `gw` rows of A (column c * P * P + py * P + px,
+// the flattening order of a Conv2d weight [N, C, P, P]) and those rows are then written whole, pad included.
+template <typename PT>
+__global__ void patchify_quantize_kernel(const PT* __restrict__ pixels, int C, int H, int W, int P, int gh, int gw,
+                                         const float* __restrict__ scale, uint8_t* __restrict__ A, long long lda,
+                                         int row_bytes) {
+    extern __shared__ __align__(16) uint8_t prep_tile[];
+    const int img = blockIdx.x / gh, gy = blockIdx.x - img * gh;
+    const int K = C * P * P;
+    const float inv = __frcp_rn(scale ? __ldg(scale) : 1.0f);
+    for (int i = threadIdx.x; i < gw * (row_bytes - K); i += blockDim.x)          // the zero pad K .. row_bytes
+        prep_tile[(i / (row_bytes - K)) * row_bytes + K + i % (row_bytes - K)] = 0;
+    const int strip = gw * P;
+    const int total = C * P * strip;
+    for (int i = threadIdx.x; i < total; i += blockDim.x) {
+        const int x = i % strip, cp = i / strip;
+        const int py = cp % P, c = cp / P;
+        const float v = prep_load(pixels + ((static_cast<long long>(img) * C + c) * H + (gy * P + py)) * W + x);
+        const int gx = x / P, px = x - gx * P;
+        prep_tile[gx * row_bytes + c * P * P + py * P + px] = prep_e4m3(v * inv);
+    }
+    __syncthreads();
+    const long long m0 = (static_cast<long long>(img) * gh + gy) * gw;
+    const int vecs = row_bytes / 16;
+    for (int i = threadIdx.x; i < gw * vecs; i += blockDim.x) {
+        const int r = i / vecs, v = i - r * vecs;
+        *reinterpret_cast<uint4*>(A + (m0 + r) * lda + 16 * v) = *reinterpret_cast<const uint4*>(prep_tile + r * row_bytes + 16 * v);
+    }
+}
+
+// |x| of non-negative floats orders like their bit patterns: one atomicMax on the bits per block.
+template <typename T>
+__global__ void amax_kernel(const T* __restrict__ x, long long rows, int cols, long long ld, unsigned* __restrict__ amax_bits) {
+    float m = 0.0f;
+    const long long total = rows * cols;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long r = i / cols;
+        m = fmaxf(m, fabsf(prep_load(x + r * ld + (i - r * cols))));
+    }
+    unsigned b = __reduce_max_sync(0xffffffffu, __float_as_uint(m));
+    __shared__ unsigned warp_max[32];
+    if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = b;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        b = threadIdx.x < (blockDim.x + 31) / 32 ? warp_max[threadIdx.x] : 0u;
+        b = __reduce_max_sync(0xffffffffu, b);
+        if (threadIdx.x == 0) atomicMax(amax_bits, b);
+    }
+}
+
+__global__ void scale_from_amax_kernel(const unsigned* __restrict__ amax_bits, float* __restrict__ scale) {
+    const float a = __uint_as_float(*amax_bits);
+    *scale = a > 0.0f ? a / 448.0f : 1.0f;                 // 448 = largest e4m3 value; an all-zero tensor keeps scale 1
+}
+
+template <typename T>
+__global__ void quantize_e4m3_kernel(const T* __restrict__ x, long long rows, int cols, long long ld,
+                                     const float* __restrict__ scale, uint8_t* __restrict__ out, long long ld_out) {
+    const float inv = __frcp_rn(scale ? __ldg(scale) : 1.0f);
+    const int groups = (cols + 7) / 8;                      // eight columns per thread: one 8-byte store
+    const long long total = rows * groups;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long r = i / groups;
+        const int c0 = static_cast<int>(i - r * groups) * 8;
+        const T* src = x + r * ld + c0;
+        uint8_t* dst = out + r * ld_out + c0;
+        if (c0 + 8 <= cols && (reinterpret_cast<uintptr_t>(dst) & 7u) == 0) {
+            uint32_t w[2];
+#pragma unroll
+            for (int h2 = 0; h2 < 2; h2++) {
+                const float a = prep_load(src + 4 * h2) * inv, b = prep_load(src + 4 * h2 + 1) * inv;
+                const float c = prep_load(src + 4 * h2 + 2) * inv, d = prep_load(src + 4 * h2 + 3) * inv;
+                w[h2] = static_cast<uint32_t>(sl8::pack_e4m3x2(a, b)) | (static_cast<uint32_t>(sl8::pack_e4m3x2(c, d)) << 16);
+            }
+            *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+        } else {
+            for (int c = c0; c < cols && c < c0 + 8; c++) dst[c - c0] = prep_e4m3(prep_load(src + (c - c0)) * inv);
+        }
+    }
+}
+
+int prep_grid(sl8_handle_t h, long long work_items) {
+    const long long want = (work_items + 255) / 256;
+    const long long cap = static_cast<long long>(h->sm_count > 0 ? h->sm_count : 148) * 16;   // a multiple of the SM count
+    return static_cast<int>(want < cap ? (want < 1 ? 1 : want) : cap);
+}
+
+}  // namespace
+
+SL8_API int sl8_patchify_quantize_e4m3(sl8_handle_t h, const void* pixels, int pixel_dtype, int images, int channels,
+                                       int height, int width, int patch, const float* scale, void* A, int64_t lda,
+                                       sl8_stream_t stream) {
+    if (!h) return SL8_ERR_INVALID_VALUE;
+    if (!pixels || !A || images < 1 || channels < 1 || patch < 1 || height < patch || width < patch)
+        return fail(h, SL8_ERR_INVALID_VALUE, "bad patchify arguments");
+    if (pixel_dtype != SL8_DT_F32 && pixel_dtype != SL8_DT_BF16) return fail(h, SL8_ERR_INVALID_VALUE, "unknown pixel dtype");
+    const int K = channels * patch * patch, gh = height / patch, gw = width / patch;
+    if (lda < K) return fail(h, SL8_ERR_INVALID_VALUE, "lda smaller than channels * patch * patch");
+    if (!aligned16(A) || lda % 16 != 0) return fail(h, SL8_ERR_ALIGNMENT, "A and lda must be multiples of 16 bytes");
+    // whole rows are written when the pad is short (K = 588 at pitch 640), else K rounded up to 16 bytes
+    const int row_bytes = static_cast<int>(lda - K < 128 ? lda : (K + 15) / 16 * 16);
+    const size_t smem = static_cast<size_t>(gw) * row_bytes;
+    if (smem > 200 * 1024) return fail(h, SL8_ERR_UNSUPPORTED, "one strip of patches exceeds 200 KiB of shared memory");
+    DeviceGuard guard(h->device);
+    if (!guard.ok) return fail(h, SL8_ERR_CUDA, "cudaSetDevice failed");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaSuccess;
+    const unsigned grid = static_cast<unsigned>(images) * gh;
+    if (pixel_dtype == SL8_DT_F32) {
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(patchify_quantize_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess)
+            patchify_quantize_kernel<float><<<grid, 256, smem, s>>>(static_cast<const float*>(pixels), channels, height, width, patch,
+                                                                    gh, gw, scale, static_cast<uint8_t*>(A), lda, row_bytes);
+    } else {
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(patchify_quantize_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess)
+            patchify_quantize_kernel<__nv_bfloat16><<<grid, 256, smem, s>>>(static_cast<const __nv_bfloat16*>(pixels), channels, height,
+                                                                            width, patch, gh, gw, scale, static_cast<uint8_t*>(A), lda, row_bytes);
+    }
+    if (e == cudaSuccess) e = cudaGetLastError();
+    return e == cudaSuccess ? SL8_OK : fail_cuda(h, e, "patchify kernel launch");
+}
+
+SL8_API int sl8_amax_scale(sl8_handle_t h, const void* x, int dtype, int64_t rows, int cols, int64_t ld, float* amax,
+                           float* scale, sl8_stream_t stream) {
+    if (!h) return SL8_ERR_INVALID_VALUE;
+    if (!x || !amax || rows < 1 || cols < 1 || ld < cols) return fail(h, SL8_ERR_INVALID_VALUE, "bad amax arguments");
+    if (dtype != SL8_DT_F32 && dtype != SL8_DT_BF16) return fail(h, SL8_ERR_INVALID_VALUE, "unknown dtype");
+    DeviceGuard guard(h->device);
+    if (!guard.ok) return fail(h, SL8_ERR_CUDA, "cudaSetDevice failed");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemsetAsync(amax, 0, sizeof(float), s);
+    if (e != cudaSuccess) return fail_cuda(h, e, "cudaMemsetAsync(amax)");
+    const int grid = prep_grid(h, rows * cols / 8);
+    if (dtype == SL8_DT_F32)
+        amax_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(x), rows, cols, ld, reinterpret_cast<unsigned*>(amax));
+    else
+        amax_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, reinterpret_cast<unsigned*>(amax));
+    if (scale) scale_from_amax_kernel<<<1, 1, 0, s>>>(reinterpret_cast<const unsigned*>(amax), scale);
+    e = cudaGetLastError();
+    return e == cudaSuccess ? SL8_OK : fail_cuda(h, e, "amax kernel launch");
+}
+
+SL8_API int sl8_quantize_e4m3(sl8_handle_t h, const void* x, int dtype, int64_t rows, int cols, int64_t ld, const float* scale,
+                              void* out, int64_t ld_out, sl8_stream_t stream) {
+    if (!h) return SL8_ERR_INVALID_VALUE;
+    if (!x || !out || rows < 1 || cols < 1 || ld < cols || ld_out < cols) return fail(h, SL8_ERR_INVALID_VALUE, "bad quantize arguments");
+    if (dtype != SL8_DT_F32 && dtype != SL8_DT_BF16) return fail(h, SL8_ERR_INVALID_VALUE, "unknown dtype");
+    DeviceGuard guard(h->device);
+    if (!guard.ok) return fail(h, SL8_ERR_CUDA, "cudaSetDevice failed");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int grid = prep_grid(h, rows * ((cols + 7) / 8));
+    if (dtype == SL8_DT_F32)
+        quantize_e4m3_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(x), rows, cols, ld, scale, static_cast<uint8_t*>(out), ld_out);
+    else
+        quantize_e4m3_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, scale,
+                                                                 static_cast<uint8_t*>(out), ld_out);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? SL8_OK : fail_cuda(h, e, "quantize kernel launch");
+}

@@ -165,6 +165,48 @@ class Engine:
             self._stream(stream)))
         return D
 
+    # ------------------------------------------------------------------ producer-side steps
+    @staticmethod
+    def _dt(x) -> int:
+        if x.dtype == torch.float32:
+            return _l.SL8_DT_F32
+        if x.dtype == torch.bfloat16:
+            return _l.SL8_DT_BF16
+        raise TypeError("expected an fp32 or bf16 tensor")
+
+    def patchify_quantize(self, pixels, patch: int, scale=None, *, out=None, pitch=None, stream=None) -> torch.Tensor:
+        """pixels [images, C, H, W] (fp32 / bf16) -> A [images * (H // patch) * (W // patch), C * patch * patch] e4m3
+        codes (uint8) at a row pitch that is a multiple of 128 bytes: the patch-embed GEMM's operand."""
+        if pixels.dim() != 4 or not pixels.is_contiguous():
+            raise ValueError("pixels must be a contiguous [images, C, H, W] tensor")
+        images, Cc, H, W = pixels.shape
+        K = Cc * patch * patch
+        rows = images * (H // patch) * (W // patch)
+        if out is None:
+            pitch = (K + 127) // 128 * 128 if pitch is None else int(pitch)
+            out = torch.empty((rows, pitch), dtype=torch.uint8, device=pixels.device)[:, :K]
+        self._check(self._lib.sl8_patchify_quantize_e4m3(
+            self._h, pixels.data_ptr(), self._dt(pixels), images, Cc, H, W, int(patch), _ptr(scale), out.data_ptr(),
+            out.stride(0), self._stream(stream)))
+        return out
+
+    def amax_scale(self, x, stream=None):
+        """(amax, scale) as one-element device tensors: max |x| and amax / 448."""
+        amax = torch.empty((1,), dtype=torch.float32, device=x.device)
+        scale = torch.empty((1,), dtype=torch.float32, device=x.device)
+        self._check(self._lib.sl8_amax_scale(self._h, x.data_ptr(), self._dt(x), x.shape[0], x.shape[1], x.stride(0),
+                                             amax.data_ptr(), scale.data_ptr(), self._stream(stream)))
+        return amax, scale
+
+    def quantize_e4m3(self, x, scale=None, *, out=None, stream=None) -> torch.Tensor:
+        """e4m3 codes (uint8) of x / scale, row pitch a multiple of 128 bytes unless `out` is given."""
+        rows, cols = x.shape
+        if out is None:
+            out = torch.empty((rows, (cols + 127) // 128 * 128), dtype=torch.uint8, device=x.device)[:, :cols]
+        self._check(self._lib.sl8_quantize_e4m3(self._h, x.data_ptr(), self._dt(x), rows, cols, x.stride(0), _ptr(scale),
+                                                out.data_ptr(), out.stride(0), self._stream(stream)))
+        return out
+
     # ------------------------------------------------------------------ host operands
     def patch_embed_host(self, A, B, table, out, *, period=None, scale_a=1.0, scale_b=1.0, row_phase=0, flags=0):
         M, K = A.shape

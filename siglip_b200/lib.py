@@ -23,6 +23,7 @@ SL8_ERR_NO_DEVICE = -7
 SL8_OUT_BF16, SL8_OUT_E4M3 = 0, 1
 SL8_OP_PATCH_EMBED, SL8_OP_FC1_GELU, SL8_OP_FC2_RESIDUAL = 0, 1, 2
 SL8_FLAG_NONE, SL8_FLAG_BIAS_F32, SL8_FLAG_PE_F32_ADD, SL8_FLAG_NO_ACTIVATION = 0, 1, 2, 4
+SL8_DT_F32, SL8_DT_BF16 = 0, 1
 
 _ERR_NAMES = {
     -1: "SL8_ERR_INVALID_VALUE", -2: "SL8_ERR_ALIGNMENT", -3: "SL8_ERR_UNSUPPORTED", -4: "SL8_ERR_CUDA",
@@ -61,6 +62,9 @@ SIGNATURES = {
     "sl8_fc1_gelu_fp8": (_I, [_P, _P, _I64, _P, _I64, _P, _P, _P, _P, _I64, _I, _P, _I64, _I, _I, _U, _P]),
     "sl8_linear_bias_fp8": (_I, [_P, _P, _I64, _P, _I64, _P, _P, _P, _P, _I64, _I, _P, _I64, _I, _I, _U, _P]),
     "sl8_fc2_residual_fp8": (_I, [_P, _P, _I64, _P, _I64, _P, _P, _P, _P, _I64, _P, _I64, _I64, _I, _I, _U, _P]),
+    "sl8_patchify_quantize_e4m3": (_I, [_P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _I64, _P]),
+    "sl8_amax_scale": (_I, [_P, _P, _I, _I64, _I, _I64, _P, _P, _P]),
+    "sl8_quantize_e4m3": (_I, [_P, _P, _I, _I64, _I, _I64, _P, _P, _I64, _P]),
     "sl8_patch_embed_fp8_host": (_I, [_P, _P, _I64, _P, _I64, _F, _F, _P, _I64, _I, _I, _I, _P, _I64, _I64, _I, _I, _U]),
     "sl8_fc1_gelu_fp8_host": (_I, [_P, _P, _I64, _P, _I64, _F, _F, _P, _P, _I64, _I, _F, _I64, _I, _I, _U]),
     "sl8_fc2_residual_fp8_host": (_I, [_P, _P, _I64, _P, _I64, _F, _F, _P, _P, _I64, _P, _I64, _I64, _I, _I, _U]),

@@ -58,6 +58,12 @@ class Oracle:
         L.sl8o_combine_bias_pos.argtypes = [_P, _P, _I, _I, _P]
         L.sl8o_quantize_e4m3.argtypes = [_P, _I64, _F, _P]
         L.sl8o_dequantize_e4m3.argtypes = [_P, _I64, _P]
+        L.sl8o_patchify_quantize.restype = _I
+        L.sl8o_patchify_quantize.argtypes = [_P, _I, _I, _I, _I, _I, _F, _P, _I64, _I]
+        L.sl8o_amax.restype = _F
+        L.sl8o_amax.argtypes = [_P, _I64, _I, _I64]
+        L.sl8o_quantize_rows_e4m3.restype = _I
+        L.sl8o_quantize_rows_e4m3.argtypes = [_P, _I64, _I, _I64, _F, _P, _I64]
 
     # ---- scalars
     def e4m3_lut(self) -> np.ndarray:
@@ -65,6 +71,27 @@ class Oracle:
 
     def num_threads(self) -> int:
         return self.lib.sl8o_num_threads()
+
+    # ---- producer-side steps; pixels / x are fp32 arrays
+    def patchify_quantize(self, pixels, patch, scale, lda, row_bytes):
+        images, Cc, H, W = pixels.shape
+        rows = images * (H // patch) * (W // patch)
+        A = np.full((rows, lda), 0xAA, dtype=np.uint8)          # what is not written stays recognisable
+        px = np.ascontiguousarray(pixels, dtype=np.float32)
+        rc = self.lib.sl8o_patchify_quantize(_np_ptr(px), images, Cc, H, W, patch, scale, _np_ptr(A), lda, row_bytes)
+        assert rc == 0
+        return A
+
+    def amax(self, x):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        return float(self.lib.sl8o_amax(_np_ptr(x), x.shape[0], x.shape[1], x.shape[1]))
+
+    def quantize_rows(self, x, scale):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        out = np.empty(x.shape, dtype=np.uint8)
+        rc = self.lib.sl8o_quantize_rows_e4m3(_np_ptr(x), x.shape[0], x.shape[1], x.shape[1], scale, _np_ptr(out), x.shape[1])
+        assert rc == 0
+        return out
 
     # ---- layers; A, B uint8 2-D (K contiguous); outputs uint16 (bf16 bits) or uint8 (e4m3 codes)
     def gemm(self, A, B):
