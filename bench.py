@@ -270,6 +270,35 @@ def layer_table(eng, dev, steps: int, peaks: dict, names=("C1", "C2", "C3", "C4"
     return out
 
 
+def prep_table(eng, dev, steps: int, peaks: dict) -> dict:
+    """The producer-side steps at the C4 / C2 sizes: HBM-bound byte work, reported against the measured copy bandwidth.
+    Algorithmic bytes: patch unfold reads the used pixels (fp32) once and writes the operand rows at their pitch;
+    abs-max reads the activation once; quantisation reads it once and writes one byte per element.  Each working
+    set exceeds the 126 MB L2."""
+    out = {}
+    images, P = 256, 14
+    g = torch.Generator(device=dev).manual_seed(0)
+    pixels = torch.rand((images, 3, 384, 384), generator=g, device=dev) * 2 - 1
+    scale = torch.tensor([1.0 / 448.0], device=dev)
+    A = eng.patchify_quantize(pixels, P, scale)
+    ms = time_steps(lambda i=0: eng.patchify_quantize(pixels, P, scale, out=A), steps, 3, lambda: None)
+    nbytes = images * 3 * (27 * P) ** 2 * 4 + A.shape[0] * A.stride(0)
+    out["patchify_quantize_C4"] = {"ms": ms, "gbs": nbytes / ms / 1e6, "frac_hbm_measured": nbytes / ms / 1e6 / peaks["hbm_gbs"],
+                                   "bytes": nbytes, "images_per_s": images / ms * 1e3}
+    del pixels, A
+    x = (torch.randn((46656, 4304), generator=g, device=dev) * 0.5).to(torch.bfloat16)
+    amax, sc = eng.amax_scale(x)
+    ms = time_steps(lambda i=0: eng.amax_scale(x), steps, 3, lambda: None)
+    nbytes = x.numel() * 2
+    out["amax_scale_C2_output"] = {"ms": ms, "gbs": nbytes / ms / 1e6, "frac_hbm_measured": nbytes / ms / 1e6 / peaks["hbm_gbs"], "bytes": nbytes}
+    q = eng.quantize_e4m3(x, sc)
+    ms = time_steps(lambda i=0: eng.quantize_e4m3(x, sc, out=q), steps, 3, lambda: None)
+    nbytes = x.numel() * 3
+    out["quantize_e4m3_C2_output"] = {"ms": ms, "gbs": nbytes / ms / 1e6, "frac_hbm_measured": nbytes / ms / 1e6 / peaks["hbm_gbs"], "bytes": nbytes}
+    eng.device_status()
+    return out
+
+
 def chain_bench(args, eng, dev, rank: int, world: int, barrier, dist) -> None:
     """C5: the MLP chain FC1 + GELU -> e4m3 -> FC2 + residual on this rank's share of 1024 images (M = 746 496
     rows in total; strong scaling: the images are divided over the ranks, no data crosses GPUs)."""
@@ -464,6 +493,7 @@ def main() -> None:
                                     "seconds": secs}
         if args.layers:
             line["layers"] = layer_table(eng, dev, max(20, min(args.steps, 100)), peaks, tuple(args.layer_names.split(",")))
+            line["prep"] = prep_table(eng, dev, max(20, min(args.steps, 100)), peaks)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

@@ -110,7 +110,8 @@ def test_linear_bias_projection(engine, oracle, M, N, K, e4m3):
         D = engine.linear_bias(p.A, p.B, p.bias, out_dtype=torch.uint8, out_scale=dscalar(0.02), **kw)
         engine.device_status()
         ref = oracle.fc1_gelu(A, B, p.scale_a, p.scale_b, bits(p.bias), out_e4m3=True, out_scale=0.02, flags=4)
-        return check_e4m3(D.cpu().numpy(), ref, f"linear-e4m3 {M}x{N}x{K}")
+        check_e4m3(D.cpu().numpy(), ref, f"linear-e4m3 {M}x{N}x{K}")
+        return
     D = engine.linear_bias(p.A, p.B, p.bias, **kw)
     engine.device_status()
     ref = oracle.fc1_gelu(A, B, p.scale_a, p.scale_b, bits(p.bias), flags=4)
