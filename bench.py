@@ -295,6 +295,14 @@ def prep_table(eng, dev, steps: int, peaks: dict) -> dict:
     ms = time_steps(lambda i=0: eng.quantize_e4m3(x, sc, out=q), steps, 3, lambda: None)
     nbytes = x.numel() * 3
     out["quantize_e4m3_C2_output"] = {"ms": ms, "gbs": nbytes / ms / 1e6, "frac_hbm_measured": nbytes / ms / 1e6 / peaks["hbm_gbs"], "bytes": nbytes}
+    del q
+    xr = torch.randn((186624, 1152), generator=g, device=dev).to(torch.bfloat16)     # 256 images of residual stream
+    gamma = torch.ones((1152,), device=dev)
+    beta = torch.zeros((1152,), device=dev)
+    ln = eng.layernorm_quantize(xr, gamma, beta, 1e-6, sc)
+    ms = time_steps(lambda i=0: eng.layernorm_quantize(xr, gamma, beta, 1e-6, sc, out=ln), steps, 3, lambda: None)
+    nbytes = xr.numel() * 3
+    out["layernorm_quantize_256_images"] = {"ms": ms, "gbs": nbytes / ms / 1e6, "frac_hbm_measured": nbytes / ms / 1e6 / peaks["hbm_gbs"], "bytes": nbytes}
     eng.device_status()
     return out
 

@@ -214,6 +214,14 @@ int sl8_amax_scale(sl8_handle_t h, const void* x, int dtype, int64_t rows, int c
 int sl8_quantize_e4m3(sl8_handle_t h, const void* x, int dtype, int64_t rows, int cols, int64_t ld,
                       const float* scale, void* out, int64_t ld_out, sl8_stream_t stream);
 
+/* LayerNorm fused with the quantisation of its output: FC1's A operand straight from the residual stream (the
+ * reference lists this fusion as unstarted, docs/architecture.md:92-101).  x [rows, cols] fp32 or bf16, gamma / beta
+ * fp32 [cols] (NULL = 1 / 0), statistics in fp32 over the row, out[r, c] = e4m3_sat_rne(((x - mean) * rsqrt(var + eps)
+ * * gamma + beta) * (1 / *scale)).  cols, ld and ld_out must be multiples of 8. */
+int sl8_layernorm_quantize_e4m3(sl8_handle_t h, const void* x, int dtype, int64_t rows, int cols, int64_t ld,
+                                const float* gamma, const float* beta, float eps, const float* scale,
+                                void* out, int64_t ld_out, sl8_stream_t stream);
+
 /* ---- the same three layers with HOST operands ------------------------------------------
  * What each reference main() does around its launch (upload operands, launch, download
  * all of C: patch_embed.cu:111-154,249-252), as one call: rows are cut into slabs that

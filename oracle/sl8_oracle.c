@@ -386,3 +386,26 @@ SL8O_API int sl8o_quantize_rows_e4m3(const float* x, int64_t rows, int cols, int
         for (int c = 0; c < cols; c++) out[r * ld_out + c] = sl8o_f32_to_e4m3(x[r * ld + c] * inv);
     return 0;
 }
+
+/* LayerNorm -> quantise (the reference lists the fusion as unstarted, docs/architecture.md:92-101): statistics in
+ * double, the affine map and the scaling in float as the device does them. */
+SL8O_API int sl8o_layernorm_quantize(const float* x, int64_t rows, int cols, int64_t ld, const float* gamma,
+                                     const float* beta, float eps, float scale, uint8_t* out, int64_t ld_out) {
+    const float inv = 1.0f / scale;
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; r++) {
+        const float* row = x + r * ld;
+        double sum = 0.0;
+        for (int c = 0; c < cols; c++) sum += row[c];
+        const double mean = sum / cols;
+        double sq = 0.0;
+        for (int c = 0; c < cols; c++) sq += (row[c] - mean) * (row[c] - mean);
+        const float rstd = (float)(1.0 / sqrt(sq / cols + (double)eps));
+        const float meanf = (float)mean;
+        for (int c = 0; c < cols; c++) {
+            const float g = gamma ? gamma[c] : 1.0f, b = beta ? beta[c] : 0.0f;
+            out[r * ld_out + c] = sl8o_f32_to_e4m3(fmaf((row[c] - meanf) * rstd, g, b) * inv);
+        }
+    }
+    return 0;
+}

@@ -950,3 +950,97 @@ SL8_API int sl8_quantize_e4m3(sl8_handle_t h, const void* x, int dtype, int64_t 
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? SL8_OK : fail_cuda(h, e, "quantize kernel launch");
 }
+
+// ---- LayerNorm -> quantise: the prologue of FC1 (docs/architecture.md:92-101 of the reference lists it as unstarted).
+// One warp per row: mean, variance (two passes, fp32, the row stays in L1 after the first), then
+// e4m3((x - mean) * rsqrt(var + eps) * gamma + beta) * (1 / scale), eight columns per lane and step.
+namespace {
+
+template <typename T>
+__device__ __forceinline__ void ln_load8(const T* p, float (&v)[8]);
+template <>
+__device__ __forceinline__ void ln_load8<float>(const float* p, float (&v)[8]) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void ln_load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 q = __ldg(reinterpret_cast<const uint4*>(p));
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+}
+
+template <typename T>
+__global__ void layernorm_quantize_kernel(const T* __restrict__ x, long long rows, int cols, long long ld,
+                                          const float* __restrict__ gamma, const float* __restrict__ beta, float eps,
+                                          const float* __restrict__ scale, uint8_t* __restrict__ out, long long ld_out) {
+    const int lane = threadIdx.x & 31;
+    const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+    const float inv = __frcp_rn(scale ? __ldg(scale) : 1.0f);
+    const float inv_n = 1.0f / static_cast<float>(cols);
+    for (long long r = warp; r < rows; r += warps) {
+        const T* row = x + r * ld;
+        float v[8];
+        float sum = 0.0f;
+        for (int c = lane * 8; c < cols; c += 256) {
+            ln_load8<T>(row + c, v);
+#pragma unroll
+            for (int i = 0; i < 8; i++) sum += v[i];
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const float mean = sum * inv_n;
+        float sq = 0.0f;
+        for (int c = lane * 8; c < cols; c += 256) {
+            ln_load8<T>(row + c, v);
+#pragma unroll
+            for (int i = 0; i < 8; i++) sq = fmaf(v[i] - mean, v[i] - mean, sq);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        const float rstd = rsqrtf(sq * inv_n + eps);
+        for (int c = lane * 8; c < cols; c += 256) {
+            ln_load8<T>(row + c, v);
+            float y[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float g = gamma ? __ldg(gamma + c + i) : 1.0f, b = beta ? __ldg(beta + c + i) : 0.0f;
+                y[i] = fmaf((v[i] - mean) * rstd, g, b) * inv;
+            }
+            const uint32_t lo = static_cast<uint32_t>(sl8::pack_e4m3x2(y[0], y[1])) | (static_cast<uint32_t>(sl8::pack_e4m3x2(y[2], y[3])) << 16);
+            const uint32_t hi = static_cast<uint32_t>(sl8::pack_e4m3x2(y[4], y[5])) | (static_cast<uint32_t>(sl8::pack_e4m3x2(y[6], y[7])) << 16);
+            *reinterpret_cast<uint2*>(out + r * ld_out + c) = make_uint2(lo, hi);
+        }
+    }
+}
+
+}  // namespace
+
+SL8_API int sl8_layernorm_quantize_e4m3(sl8_handle_t h, const void* x, int dtype, int64_t rows, int cols, int64_t ld,
+                                        const float* gamma, const float* beta, float eps, const float* scale, void* out,
+                                        int64_t ld_out, sl8_stream_t stream) {
+    if (!h) return SL8_ERR_INVALID_VALUE;
+    if (!x || !out || rows < 1 || cols < 1 || ld < cols || ld_out < cols || !(eps >= 0.0f))
+        return fail(h, SL8_ERR_INVALID_VALUE, "bad layernorm arguments");
+    if (dtype != SL8_DT_F32 && dtype != SL8_DT_BF16) return fail(h, SL8_ERR_INVALID_VALUE, "unknown dtype");
+    if (cols % 8 != 0 || ld % 8 != 0 || ld_out % 8 != 0) return fail(h, SL8_ERR_UNSUPPORTED, "cols, ld and ld_out must be multiples of 8");
+    if (!aligned16(x) || (reinterpret_cast<uintptr_t>(out) & 7u) != 0 || (gamma && !aligned16(gamma)) || (beta && !aligned16(beta)))
+        return fail(h, SL8_ERR_ALIGNMENT, "x, gamma, beta must be 16-byte aligned and out 8-byte aligned");
+    DeviceGuard guard(h->device);
+    if (!guard.ok) return fail(h, SL8_ERR_CUDA, "cudaSetDevice failed");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int grid = prep_grid(h, rows * 32);            // one warp per row, eight warps per block
+    if (dtype == SL8_DT_F32)
+        layernorm_quantize_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(x), rows, cols, ld, gamma, beta, eps, scale,
+                                                              static_cast<uint8_t*>(out), ld_out);
+    else
+        layernorm_quantize_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, gamma, beta,
+                                                                      eps, scale, static_cast<uint8_t*>(out), ld_out);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? SL8_OK : fail_cuda(h, e, "layernorm kernel launch");
+}

@@ -207,6 +207,16 @@ class Engine:
                                                 out.data_ptr(), out.stride(0), self._stream(stream)))
         return out
 
+    def layernorm_quantize(self, x, gamma=None, beta=None, eps: float = 1e-6, scale=None, *, out=None, stream=None) -> torch.Tensor:
+        """e4m3 codes (uint8) of LayerNorm(x) / scale: FC1's A operand, row pitch a multiple of 128 bytes."""
+        rows, cols = x.shape
+        if out is None:
+            out = torch.empty((rows, (cols + 127) // 128 * 128), dtype=torch.uint8, device=x.device)[:, :cols]
+        self._check(self._lib.sl8_layernorm_quantize_e4m3(
+            self._h, x.data_ptr(), self._dt(x), rows, cols, x.stride(0), _ptr(gamma), _ptr(beta), float(eps), _ptr(scale),
+            out.data_ptr(), out.stride(0), self._stream(stream)))
+        return out
+
     # ------------------------------------------------------------------ host operands
     def patch_embed_host(self, A, B, table, out, *, period=None, scale_a=1.0, scale_b=1.0, row_phase=0, flags=0):
         M, K = A.shape

@@ -65,6 +65,7 @@ SIGNATURES = {
     "sl8_patchify_quantize_e4m3": (_I, [_P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _I64, _P]),
     "sl8_amax_scale": (_I, [_P, _P, _I, _I64, _I, _I64, _P, _P, _P]),
     "sl8_quantize_e4m3": (_I, [_P, _P, _I, _I64, _I, _I64, _P, _P, _I64, _P]),
+    "sl8_layernorm_quantize_e4m3": (_I, [_P, _P, _I, _I64, _I, _I64, _P, _P, _F, _P, _P, _I64, _P]),
     "sl8_patch_embed_fp8_host": (_I, [_P, _P, _I64, _P, _I64, _F, _F, _P, _I64, _I, _I, _I, _P, _I64, _I64, _I, _I, _U]),
     "sl8_fc1_gelu_fp8_host": (_I, [_P, _P, _I64, _P, _I64, _F, _F, _P, _P, _I64, _I, _F, _I64, _I, _I, _U]),
     "sl8_fc2_residual_fp8_host": (_I, [_P, _P, _I64, _P, _I64, _F, _F, _P, _P, _I64, _P, _I64, _I64, _I, _I, _U]),

@@ -64,6 +64,8 @@ class Oracle:
         L.sl8o_amax.argtypes = [_P, _I64, _I, _I64]
         L.sl8o_quantize_rows_e4m3.restype = _I
         L.sl8o_quantize_rows_e4m3.argtypes = [_P, _I64, _I, _I64, _F, _P, _I64]
+        L.sl8o_layernorm_quantize.restype = _I
+        L.sl8o_layernorm_quantize.argtypes = [_P, _I64, _I, _I64, _P, _P, _F, _F, _P, _I64]
 
     # ---- scalars
     def e4m3_lut(self) -> np.ndarray:
@@ -90,6 +92,16 @@ class Oracle:
         x = np.ascontiguousarray(x, dtype=np.float32)
         out = np.empty(x.shape, dtype=np.uint8)
         rc = self.lib.sl8o_quantize_rows_e4m3(_np_ptr(x), x.shape[0], x.shape[1], x.shape[1], scale, _np_ptr(out), x.shape[1])
+        assert rc == 0
+        return out
+
+    def layernorm_quantize(self, x, gamma, beta, eps, scale):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        g = np.ascontiguousarray(gamma, dtype=np.float32)
+        b = np.ascontiguousarray(beta, dtype=np.float32)
+        out = np.empty(x.shape, dtype=np.uint8)
+        rc = self.lib.sl8o_layernorm_quantize(_np_ptr(x), x.shape[0], x.shape[1], x.shape[1], _np_ptr(g), _np_ptr(b), eps, scale,
+                                              _np_ptr(out), x.shape[1])
         assert rc == 0
         return out
 

@@ -151,3 +151,60 @@ def test_prep_argument_checks(engine):
         engine.patchify_quantize(px, 14, out=narrow)                                 # row pitch 512 < K = 588
     with pytest.raises(TypeError):
         engine.amax_scale(torch.zeros((2, 2), dtype=torch.float16, device=DEV))
+
+
+def test_oracle_layernorm_quantize_against_numpy(oracle):
+    rng = np.random.default_rng(2)
+    x = (rng.standard_normal((33, 1152)) * 1.7 + 0.3).astype(np.float32)
+    gamma = (1.0 + 0.1 * rng.standard_normal(1152)).astype(np.float32)
+    beta = (0.05 * rng.standard_normal(1152)).astype(np.float32)
+    scale, eps = 0.01, 1e-6
+    q = oracle.layernorm_quantize(x, gamma, beta, eps, scale)
+    xd = x.astype(np.float64)
+    mean = xd.mean(axis=1, keepdims=True)
+    var = ((xd - mean) ** 2).mean(axis=1, keepdims=True)
+    y = (xd - mean) / np.sqrt(var + eps) * gamma + beta
+    want = nearest_e4m3(oracle, (y / scale).astype(np.float32))
+    lut = oracle.e4m3_lut()
+    same = q == want
+    assert same.mean() > 0.999                               # float vs double intermediates: a rounding tie now and then
+    assert np.all(np.abs(lut[q] - lut[want]) <= np.maximum(np.abs(lut[want]) * 0.13, 2.0 ** -9))   # never more than one code
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,cols", [(1000, 1152), (77, 768), (5, 4304 - 4304 % 8)])
+def test_layernorm_quantize_on_gpu(engine, oracle, dtype, rows, cols):
+    from tests.tolerance import check_e4m3
+    g = torch.Generator(device=DEV).manual_seed(rows * 7 + cols)
+    x = (torch.randn((rows, cols), generator=g, device=DEV) * 1.5 + 0.25).to(dtype)
+    gamma = 1.0 + 0.1 * torch.randn((cols,), generator=g, device=DEV)
+    beta = 0.05 * torch.randn((cols,), generator=g, device=DEV)
+    scale = torch.tensor([0.0125], device=DEV)
+    q = engine.layernorm_quantize(x, gamma, beta, 1e-6, scale)
+    engine.device_status()
+    ref = oracle.layernorm_quantize(x.float().cpu().numpy(), gamma.cpu().numpy(), beta.cpu().numpy(), 1e-6, float(scale.item()))
+    check_e4m3(q.cpu().numpy(), ref, f"layernorm-quantize {rows}x{cols}")
+    assert q.stride(0) % 128 == 0
+    plain = engine.layernorm_quantize(x, None, None, 1e-6, scale)                  # gamma = 1, beta = 0
+    ref_plain = oracle.layernorm_quantize(x.float().cpu().numpy(), np.ones(cols, np.float32), np.zeros(cols, np.float32), 1e-6,
+                                          float(scale.item()))
+    check_e4m3(plain.cpu().numpy(), ref_plain, "layernorm-quantize without affine")
+
+
+@pytest.mark.gpu
+def test_layernorm_quantize_feeds_fc1(engine, oracle):
+    """Residual stream -> LayerNorm -> e4m3 -> FC1, against the oracle's FC1 on the codes the kernel produced."""
+    from siglip_b200 import synth
+    from tests.tolerance import check_bf16
+    M = 500
+    g = torch.Generator(device=DEV).manual_seed(9)
+    x = torch.randn((M, 1152), generator=g, device=DEV).to(torch.bfloat16)
+    scale = torch.tensor([4.0 / 448.0], device=DEV)
+    A = engine.layernorm_quantize(x, None, None, 1e-6, scale)
+    p = synth.make_fc1(M, 4304, 1152, seed=10, device=DEV)
+    D = engine.fc1_gelu(A, p.B, p.bias, scale_a=scale, scale_b=torch.tensor([p.scale_b], device=DEV))
+    engine.device_status()
+    ref = oracle.fc1_gelu(np.ascontiguousarray(A.cpu().numpy()), p.B.cpu().numpy(), float(scale.item()), p.scale_b,
+                          p.bias.view(torch.uint16).cpu().numpy())
+    check_bf16(D.view(torch.uint16).cpu().numpy(), ref, "layernorm -> fc1")
