@@ -14,7 +14,7 @@ reference's own binaries, ``siglip_b200/lib/siglip_bench``), given as ``name=com
 
     python -m siglip_b200.compare --op fc2 --M 46656 --N 1152 --K 4304 --runs 10 \\
         --arms ours,ours:v13,cublaslt,cublaslt_unfused
-    python -m siglip_b200.compare --runs 5 --arms "new=siglip_b200/lib/siglip_bench --op fc1,ref=oracle/_ref/fc1-gelu"
+    python -m siglip_b200.compare --runs 5 --arms "new=siglip_b200/lib/siglip_bench --layer fc1,ref=oracle/_ref/fc1-gelu"
 
 Arms are interleaved run by run so that clock and thermal drift hit all of them alike.
 """
