@@ -31,7 +31,8 @@ import torch
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-METRIC = "fp8_tflops_fc1_gelu"
+METRIC = "fp8_tflops_fc1_gelu"          # the default workload (C2); other --config values name their own layer
+METRICS = {"C1": "fp8_tflops_patch_embed", "C2": METRIC, "C3": "fp8_tflops_fc2_residual", "C4": "fp8_tflops_patch_embed"}
 UNIT = "TFLOP/s"
 
 
@@ -153,7 +154,7 @@ def reference_arm(args, rank: int, world: int) -> None:
     value = sum(vals) / len(vals)
     flops = 2.0 * c["M"] * c["N"] * c["K"]
     line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "impl": "reference", "metric": METRICS.get(args.config, METRIC), "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": flops / (value * 1e12) * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(args.config),
@@ -469,7 +470,7 @@ def main() -> None:
 
     if rank == 0:
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "metric": METRICS.get(args.config, METRIC), "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_max, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "e4m3 x e4m3 -> f32", "data": "synthetic", "config": workload_config(args.config, args.images),
             "clocks": clocks, "gpu_launches": args.steps,

@@ -110,8 +110,13 @@ struct DeviceGuard {
 // ---- dispatch -------------------------------------------------------------------------
 // The table is generated from a sweep on B200 (python -m siglip_b200.sweep); shapes it does not hold fall back
 // to rules (one line per rule; the first match wins).
+int kernel_slot(int op, int out_dtype) {
+    if (op == SL8_OP_PATCH_EMBED) return sl8::K_PE;
+    if (op == SL8_OP_FC2_RESIDUAL) return sl8::K_FC2;
+    return out_dtype == SL8_OUT_E4M3 ? sl8::K_FC1_E4M3 : sl8::K_FC1_BF16;
+}
+
 int pick_variant(int op, int out_dtype, long long M, int N, int K) {
-    (void)out_dtype;
     // A (layer, N, K) the committed sweep covers: the row with the largest m_min <= M decides.
     int swept = -1;
     long long swept_m = -1;
@@ -122,7 +127,8 @@ int pick_variant(int op, int out_dtype, long long M, int N, int K) {
             swept_m = r.m_min;
         }
     }
-    if (swept >= 0 && swept < SL8_NUM_VARIANTS) return swept;
+    // (the sweep times bf16 outputs; a variant that has no kernel for this output type is passed over)
+    if (swept >= 0 && swept < SL8_NUM_VARIANTS && variant(swept) && variant(swept)->kernel[kernel_slot(op, out_dtype)]) return swept;
     // Any other shape: the rules the sweeps suggest.
     const long long tiles256 = ((M + 255) / 256) * ((N + 255) / 256);
     if (tiles256 < 37) {
@@ -197,12 +203,6 @@ int validate(sl8_handle_t h, const Problem& q) {
     return SL8_OK;
 }
 
-int kernel_slot(int op, int out_dtype) {
-    if (op == SL8_OP_PATCH_EMBED) return sl8::K_PE;
-    if (op == SL8_OP_FC2_RESIDUAL) return sl8::K_FC2;
-    return out_dtype == SL8_OUT_E4M3 ? sl8::K_FC1_E4M3 : sl8::K_FC1_BF16;
-}
-
 int encode_2d(sl8_handle_t h, CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* base,
               unsigned long long inner, unsigned long long outer, unsigned long long pitch_bytes, unsigned box_inner,
               unsigned box_outer, CUtensorMapL2promotion promo) {
@@ -261,7 +261,7 @@ int run(sl8_handle_t h, const Problem& q, cudaStream_t stream) {
     if (!v) return fail(h, SL8_ERR_INVALID_VALUE, "no such kernel variant");
     const int slot = kernel_slot(q.op, q.out_dtype);
     const int ob = (q.out_dtype == SL8_OUT_BF16) ? 2 : 1;
-    if (!v->kernel[slot]) return fail(h, SL8_ERR_UNSUPPORTED, "the forced kernel variant has one staging buffer and serves FC1 only");
+    if (!v->kernel[slot]) return fail(h, SL8_ERR_UNSUPPORTED, "the forced kernel variant does not serve this layer / output type");
 
     if (!h->smem_attr_set[vid][slot]) {
         cudaError_t e = cudaFuncSetAttribute(v->kernel[slot], cudaFuncAttributeMaxDynamicSharedMemorySize, v->smem_bytes[slot]);

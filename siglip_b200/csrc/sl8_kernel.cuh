@@ -116,7 +116,7 @@ template <int CG, int TN, int TK, int STAGES, int EPI_WARPS, int OUT, int NBUF>
 struct KernelTraits {
     static_assert(CG == 1 || CG == 2, "one CTA or a CTA pair per tile");
     static_assert(TN == 128 || TN == 256, "tile N");
-    static_assert(EPI_WARPS == 4 || EPI_WARPS == 8, "one or two warps per TMEM lane quadrant");
+    static_assert(EPI_WARPS == 4 || EPI_WARPS == 8 || EPI_WARPS == 16, "one, two or four warps per TMEM lane quadrant");
     static_assert(NBUF >= 1 && NBUF <= 4, "staging buffers per epilogue warp");
     static constexpr int TILE_M_CTA = 128;                       // rows per CTA = TMEM lanes
     static_assert(TK == 128 || TK == 256, "bytes of K per stage: one or two 128-byte swizzle atoms");

@@ -1,6 +1,8 @@
 // sl8_variant.cu -- instantiates the four kernels (patch-embed, FC1 -> bf16, FC1 -> e4m3,
 // FC2) of ONE tile configuration and exports its table entry.  Compiled once per entry of
 // SL8_VARIANT_LIST with -DSL8_VARIANT_ID=<id>, so the configurations build in parallel.
+#include <type_traits>
+
 #include "sl8_variants.h"
 
 #ifndef SL8_VARIANT_ID
@@ -45,14 +47,15 @@ template <int ID, int CG, int TN, int TK, int STAGES, int EW, int NBUF>
 const VariantEntry* make_entry() {
     constexpr bool SIDE = NBUF >= 2;   // layers with side data need a second staging buffer
     using T16 = KernelTraits<CG, TN, TK, STAGES, EW, OUT_BF16, NBUF>;
-    using T8 = KernelTraits<CG, TN, TK, STAGES, EW, OUT_E4M3, NBUF>;
+    constexpr bool E4 = (TN / (EW / 4)) % 128 == 0;   // an e4m3 staging region is 128 columns wide
+    using T8 = std::conditional_t<E4, KernelTraits<CG, TN, TK, STAGES, EW, E4 ? OUT_E4M3 : OUT_BF16, NBUF>, T16>;
     static const VariantEntry e = {
         ID, CG, TN, TK, STAGES, EW, NBUF, T16::THREADS,
         {T16::SMEM_BYTES, T16::SMEM_BYTES, T8::SMEM_BYTES, T16::SMEM_BYTES},
         {Slot<CG, TN, TK, STAGES, EW, OP_PE, OUT_BF16, NBUF, SIDE>::kernel(), Slot<CG, TN, TK, STAGES, EW, OP_FC1, OUT_BF16, NBUF, true>::kernel(),
-         Slot<CG, TN, TK, STAGES, EW, OP_FC1, OUT_E4M3, NBUF, true>::kernel(), Slot<CG, TN, TK, STAGES, EW, OP_FC2, OUT_BF16, NBUF, SIDE>::kernel()},
+         Slot<CG, TN, TK, STAGES, EW, OP_FC1, OUT_E4M3, NBUF, E4>::kernel(), Slot<CG, TN, TK, STAGES, EW, OP_FC2, OUT_BF16, NBUF, SIDE>::kernel()},
         {Slot<CG, TN, TK, STAGES, EW, OP_PE, OUT_BF16, NBUF, SIDE>::launcher(), Slot<CG, TN, TK, STAGES, EW, OP_FC1, OUT_BF16, NBUF, true>::launcher(),
-         Slot<CG, TN, TK, STAGES, EW, OP_FC1, OUT_E4M3, NBUF, true>::launcher(), Slot<CG, TN, TK, STAGES, EW, OP_FC2, OUT_BF16, NBUF, SIDE>::launcher()}};
+         Slot<CG, TN, TK, STAGES, EW, OP_FC1, OUT_E4M3, NBUF, E4>::launcher(), Slot<CG, TN, TK, STAGES, EW, OP_FC2, OUT_BF16, NBUF, SIDE>::launcher()}};
     return &e;
 }
 

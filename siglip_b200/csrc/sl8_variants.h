@@ -32,9 +32,10 @@
     X(10, 2, 256, 256, 2, 4, 4)  \
     X(11, 2, 256, 256, 2, 8, 2)  \
     X(12, 2, 256, 128, 3, 8, 3)  \
-    X(13, 2, 256, 128, 4, 4, 3)
+    X(13, 2, 256, 128, 4, 4, 3)  \
+    X(14, 2, 256, 128, 4, 16, 1)
 
-#define SL8_NUM_VARIANTS 14
+#define SL8_NUM_VARIANTS 15
 
 namespace sl8 {
 
