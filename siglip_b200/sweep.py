@@ -75,7 +75,7 @@ def prune(variants: list[dict], op: int, resources: dict | None = None, out_dtyp
 
 
 # ----------------------------------------------------------------------------- table (CPU)
-def best_rows(rows: list[dict], keep_margin: float = 0.03) -> list[dict]:
+def best_rows(rows: list[dict], keep_margin: float = 0.02) -> list[dict]:
     """CSV rows -> dispatch rows {op, N, K, m_min, variant}.
 
     Per (op, N, K) the M ladder is walked upwards; the winner of the previous (smaller) M is kept unless
