@@ -62,7 +62,20 @@ struct HostPipe {
 
 }  // namespace
 
+// Tensor maps of recent calls, keyed by everything that goes into one: a layer called again on the same buffers
+// (every step of a model) skips the four driver encodes, which cost more host time than the launch itself.
+struct MapCacheEntry {
+    int dt = -1, promo = 0;
+    const void* base = nullptr;
+    unsigned long long inner = 0, outer = 0, pitch = 0;
+    unsigned box_inner = 0, box_outer = 0;
+    CUtensorMap map;
+};
+
 struct sl8_context {
+    static constexpr int kMapCache = 32;
+    MapCacheEntry map_cache[kMapCache];
+    int map_cache_next = 0;
     int device = 0;
     int sm_count = 0;
     uint32_t* d_status = nullptr;       // 4 words
@@ -206,6 +219,14 @@ int validate(sl8_handle_t h, const Problem& q) {
 int encode_2d(sl8_handle_t h, CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* base,
               unsigned long long inner, unsigned long long outer, unsigned long long pitch_bytes, unsigned box_inner,
               unsigned box_outer, CUtensorMapL2promotion promo) {
+    for (int i = 0; i < sl8_context::kMapCache; i++) {      // callers hold h->mu
+        const MapCacheEntry& c = h->map_cache[i];
+        if (c.base == base && c.dt == (int)dt && c.promo == (int)promo && c.inner == inner && c.outer == outer &&
+            c.pitch == pitch_bytes && c.box_inner == box_inner && c.box_outer == box_outer) {
+            *map = c.map;
+            return SL8_OK;
+        }
+    }
     cuuint64_t dims[2] = {inner, outer};
     cuuint64_t strides[1] = {pitch_bytes};
     cuuint32_t box[2] = {box_inner, box_outer};
@@ -213,6 +234,12 @@ int encode_2d(sl8_handle_t h, CUtensorMap* map, CUtensorMapDataType dt, int elem
     (void)elem_bytes;
     CUresult r = h->encode(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                            CU_TENSOR_MAP_SWIZZLE_128B, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS) {
+        MapCacheEntry& c = h->map_cache[h->map_cache_next];
+        h->map_cache_next = (h->map_cache_next + 1) % sl8_context::kMapCache;
+        c.dt = (int)dt; c.promo = (int)promo; c.base = base; c.inner = inner; c.outer = outer; c.pitch = pitch_bytes;
+        c.box_inner = box_inner; c.box_outer = box_outer; c.map = *map;
+    }
     if (r != CUDA_SUCCESS) {
         char buf[160];
         snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled failed (CUresult %d) dims {%llu,%llu} pitch %llu box {%u,%u}",
