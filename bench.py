@@ -265,6 +265,13 @@ def layer_table(eng, dev, steps: int, peaks: dict, names=("C1", "C2", "C3", "C4"
                      "images_per_s": synth.CONFIGS[name]["images"] / ms * 1e3}
         del fn
         torch.cuda.empty_cache()
+        if name == "C2":   # the opt-in GELU through the hardware tanh (SL8_FLAG_GELU_HW_TANH = 8), for information
+            sa_, sb_ = torch.tensor([p.scale_a], device=dev), torch.tensor([p.scale_b], device=dev)
+            d_ = torch.empty((p.M, p.N), dtype=torch.bfloat16, device=dev)
+            ms_fast = time_steps(lambda i=0: eng.fc1_gelu(p.A, p.B, p.bias, scale_a=sa_, scale_b=sb_, out=d_, flags=8), steps, 3, lambda: None)
+            out[name]["hw_tanh_gelu_ms"] = ms_fast
+            out[name]["hw_tanh_gelu_tflops"] = p.flops() / ms_fast / 1e9
+            del d_
         out[name].update(cublaslt_baseline(p, dev, steps))
         del p
         torch.cuda.empty_cache()

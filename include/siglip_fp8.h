@@ -82,7 +82,10 @@ enum {
      * bf16-domain add of bf16(acc) and the table (patch_embed.cu:44-58). */
     SL8_FLAG_PE_F32_ADD  = 2,
     /* FC1 entry points: no activation, D = acc * scale + bias (what sl8_linear_bias_fp8 sets). */
-    SL8_FLAG_NO_ACTIVATION = 4
+    SL8_FLAG_NO_ACTIVATION = 4,
+    /* FC1: GELU through the hardware tanh (tanh.approx.f32, relative error ~2^-11): one special-function operation
+     * per element instead of two.  |error| <= ~2.5e-4 |x| against the exact form; off by default. */
+    SL8_FLAG_GELU_HW_TANH = 8
 };
 
 /* Which kernel variant the dispatch table picks for a problem. */

@@ -186,10 +186,12 @@ int validate(sl8_handle_t h, const Problem& q) {
 #else
     constexpr unsigned kDiagBits = 0u;
 #endif
-    if (q.flags & ~(unsigned)(SL8_FLAG_BIAS_F32 | SL8_FLAG_PE_F32_ADD | SL8_FLAG_NO_ACTIVATION | kDiagBits))
+    if (q.flags & ~(unsigned)(SL8_FLAG_BIAS_F32 | SL8_FLAG_PE_F32_ADD | SL8_FLAG_NO_ACTIVATION | SL8_FLAG_GELU_HW_TANH | kDiagBits))
         return fail(h, SL8_ERR_INVALID_VALUE, "unknown flag bits");
-    if ((q.flags & SL8_FLAG_NO_ACTIVATION) && q.op != SL8_OP_FC1_GELU)
-        return fail(h, SL8_ERR_INVALID_VALUE, "SL8_FLAG_NO_ACTIVATION belongs to the FC1 entry points");
+    if ((q.flags & (SL8_FLAG_NO_ACTIVATION | SL8_FLAG_GELU_HW_TANH)) && q.op != SL8_OP_FC1_GELU)
+        return fail(h, SL8_ERR_INVALID_VALUE, "SL8_FLAG_NO_ACTIVATION / SL8_FLAG_GELU_HW_TANH belong to the FC1 entry points");
+    if ((q.flags & SL8_FLAG_NO_ACTIVATION) && (q.flags & SL8_FLAG_GELU_HW_TANH))
+        return fail(h, SL8_ERR_INVALID_VALUE, "SL8_FLAG_NO_ACTIVATION and SL8_FLAG_GELU_HW_TANH exclude each other");
     if (q.N % 16 != 0) return fail(h, SL8_ERR_UNSUPPORTED, "N must be a multiple of 16");
     if (q.lda < q.K || q.ldb < q.K) return fail(h, SL8_ERR_INVALID_VALUE, "lda / ldb smaller than K");
     if (q.ldd < q.N) return fail(h, SL8_ERR_INVALID_VALUE, "ldd smaller than N");

@@ -22,7 +22,7 @@ SL8_ERR_NO_DEVICE = -7
 
 SL8_OUT_BF16, SL8_OUT_E4M3 = 0, 1
 SL8_OP_PATCH_EMBED, SL8_OP_FC1_GELU, SL8_OP_FC2_RESIDUAL = 0, 1, 2
-SL8_FLAG_NONE, SL8_FLAG_BIAS_F32, SL8_FLAG_PE_F32_ADD, SL8_FLAG_NO_ACTIVATION = 0, 1, 2, 4
+SL8_FLAG_NONE, SL8_FLAG_BIAS_F32, SL8_FLAG_PE_F32_ADD, SL8_FLAG_NO_ACTIVATION, SL8_FLAG_GELU_HW_TANH = 0, 1, 2, 4, 8
 SL8_DT_F32, SL8_DT_BF16 = 0, 1
 
 _ERR_NAMES = {

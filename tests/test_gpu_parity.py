@@ -12,7 +12,7 @@ import torch
 
 from siglip_b200 import synth
 from siglip_b200.layers import num_variants, describe_variant
-from tests.tolerance import check_bf16, check_e4m3
+from tests.tolerance import bf16_bits_to_f32, check_bf16, check_e4m3
 
 pytestmark = pytest.mark.gpu
 
@@ -119,6 +119,24 @@ def test_linear_bias_projection(engine, oracle, M, N, K, e4m3):
     # and it is not the GELU layer
     G = engine.fc1_gelu(p.A, p.B, p.bias, **kw)
     assert not torch.equal(G, D)
+
+
+def test_fc1_hardware_tanh_gelu_is_inside_the_stated_tolerance(engine, oracle):
+    """SL8_FLAG_GELU_HW_TANH: not bit-comparable to the exact form, but inside |err| <= 1e-2 |ref| + 1.5e-3 (the hardware
+    tanh is good to ~2^-11 relative, so the error of 0.5 x (1 + tanh u) stays under ~2.5e-4 |x|)."""
+    M, N, K = 729, 4304, 1152
+    p = synth.make_fc1(M, N, K, seed=77, device=DEV)
+    kw = dict(scale_a=dscalar(p.scale_a), scale_b=dscalar(p.scale_b))
+    D = engine.fc1_gelu(p.A, p.B, p.bias, flags=8, **kw)
+    engine.device_status()
+    ref = oracle.fc1_gelu(p.A.cpu().numpy(), p.B.cpu().numpy(), p.scale_a, p.scale_b, bits(p.bias))
+    got = bf16_bits_to_f32(bits(D)).astype(np.float64)
+    want = bf16_bits_to_f32(ref).astype(np.float64)
+    err = np.abs(got - want)
+    assert np.all(err <= 1e-2 * np.abs(want) + 1.5e-3), float(err.max())
+    exact = float(np.mean(bits(D) == ref))
+    assert exact > 0.80                                   # most roundings still agree; the default path is held to 0.99
+    print(f"hardware-tanh GELU: max |err| {err.max():.2e}, bit-identical {exact:.4f}")
 
 
 def test_no_activation_flag_is_refused_outside_fc1(engine):
