@@ -11,8 +11,10 @@
 // plus "Custom kernel: %.3f ms" for tools/stat_test.py:27.  Shapes are run-time here:
 //
 //     siglip_bench --layer pe|fc1|fc2 [--M rows] [--N n] [--K k] [--period p] [--runs r]
+//     siglip_bench --config C1|C2|C3|C4            (the benchmark configurations: layer and shape in one word)
 //
 // Defaults are the reference's: M = 928256, patch-embed 768 x 768 period 196, FC1 3072 x 768, FC2 768 x 3072.
+// A JSON line with the same figures follows the @@RESULT line.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -70,8 +72,16 @@ int main(int argc, char** argv) {
         else if (!strcmp(argv[i], "--K") && i + 1 < argc) K = atoi(argv[++i]);
         else if (!strcmp(argv[i], "--period") && i + 1 < argc) period = atoi(argv[++i]);
         else if (!strcmp(argv[i], "--runs") && i + 1 < argc) runs = atoi(argv[++i]);
+        else if (!strcmp(argv[i], "--config") && i + 1 < argc) {
+            const char* c = argv[++i];
+            if (!strcmp(c, "C1")) { layer = "pe"; M = 6272; N = 768; K = 768; period = 196; }
+            else if (!strcmp(c, "C2")) { layer = "fc1"; M = 46656; N = 4304; K = 1152; }
+            else if (!strcmp(c, "C3")) { layer = "fc2"; M = 46656; N = 1152; K = 4304; }
+            else if (!strcmp(c, "C4")) { layer = "pe"; M = 186624; N = 1152; K = 588; period = 729; }
+            else { fprintf(stderr, "unknown config %s (C1..C4)\n", c); return 2; }
+        }
         else {
-            fprintf(stderr, "usage: %s --layer pe|fc1|fc2 [--M rows] [--N n] [--K k] [--period p] [--runs r]\n", argv[0]);
+            fprintf(stderr, "usage: %s [--config C1|C2|C3|C4] [--layer pe|fc1|fc2] [--M rows] [--N n] [--K k] [--period p] [--runs r]\n", argv[0]);
             return 2;
         }
     }
@@ -187,6 +197,8 @@ int main(int argc, char** argv) {
     // the reference's parsers accept [0-9.] only: a non-negative fixed-notation checksum and |c0|
     printf("@@RESULT ms=%.3f tflops=%.2f checksum=%f valid=%d c0=%.1f\n", ms, tflops, cksum, valid,
            std::fabs(__bfloat162float(hC[0])));
+    printf("{\"layer\": \"%s\", \"M\": %lld, \"N\": %d, \"K\": %d, \"ms\": %.4f, \"tflops\": %.2f, \"valid\": %d, \"variant\": %d, "
+           "\"runs\": %d, \"operands\": \"reference constants\"}\n", layer, M, N, K, ms, tflops, valid, cfg.variant_id, runs);
 
     cudaFree(d_A); cudaFree(d_B); cudaFree(d_bias); cudaFree(d_C);
     if (d_pos) cudaFree(d_pos);

@@ -32,3 +32,14 @@ def test_bench_host_protocol(layer, extra):
     assert valid == 1 and ms > 0 and tflops > 0 and checksum > 0
     if layer == "pe" and not extra:
         assert c0 == 1728.0        # 768 * 2.25 + bf16(1 + 3), rounded to even: the reference prints the same c0
+
+
+@pytest.mark.parametrize("config,layer,N", [("C1", "pe", 768), ("C3", "fc2", 1152)])
+def test_bench_host_named_configs_and_json_line(config, layer, N):
+    import json
+    out = subprocess.run([str(BENCH), "--config", config, "--runs", "3"], capture_output=True, text=True, timeout=300)
+    text = out.stdout + out.stderr
+    assert out.returncode == 0, text[-2000:]
+    js = [json.loads(l) for l in text.splitlines() if l.startswith("{")]
+    assert len(js) == 1 and js[0]["layer"] == layer and js[0]["N"] == N and js[0]["valid"] == 1 and js[0]["tflops"] > 0
+    assert re.search(GRID_SEARCH_RE, text)
