@@ -82,7 +82,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         objs.append(o)
         jobs.append(([exe, *NVCC_FLAGS, f"-DSL8_VARIANT_ID={vid}", "-c", str(CSRC / "sl8_variant.cu"), "-o", str(o)],
                      OBJ / f"variant_{vid}.log", verbose))
-    for name in ("api", "static"):
+    for name in ("api", "static", "prep"):
         o = OBJ / f"{name}.o"
         objs.append(o)
         jobs.append(([exe, *NVCC_FLAGS, "-c", str(CSRC / f"sl8_{name}.cu"), "-o", str(o)], OBJ / f"{name}.log", verbose))
