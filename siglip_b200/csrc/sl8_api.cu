@@ -85,7 +85,8 @@ int pick_variant(int op, int out_dtype, long long M, int N, int K) {
     // A tcgen05.mma of a CTA pair takes about 150 cycles whatever its N (measured for N = 128, 192,
     // 256), so the widest tile does the most work per instruction even where N = 1152 leaves the
     // fifth 256-wide tile half empty.
-    if (op == SL8_OP_FC1_GELU) return 2;      // GELU epilogue: two epilogue warps per scheduler
+    if (op == SL8_OP_FC1_GELU)                // GELU epilogue: four epilogue warps per scheduler (bf16 out), else two
+        return out_dtype == SL8_OUT_BF16 ? 15 : 2;
     if (op == SL8_OP_PATCH_EMBED) return 5;   // short K: four staging boxes keep the table loads ahead of the epilogue
     return 1;
 }

@@ -138,7 +138,11 @@ struct KernelTraits {
     static constexpr int REGIONS_PER_TILE = COLS_PER_WARP / REGION_COLS;
     static constexpr int CHUNKS_PER_REGION = REGION_COLS / 32;   // 32-column tcgen05.ld chunks per region
     static constexpr int BAR_BYTES = 512;                        // pipeline barriers + two per staging box
-    static constexpr int BIAS_BYTES = EPI_WARPS * COLS_PER_WARP * 4;   // fp32 bias of the current tile, one copy per warp
+    // fp32 bias of the current tile: one copy per epilogue warp in shared memory (broadcast reads) where that fits;
+    // a configuration that needs every byte for the operand ring keeps it in registers instead (lane l holds the
+    // bias of column l of each 32-column chunk) and broadcasts by warp shuffle.
+    static constexpr bool BIAS_IN_SMEM = 1024 + STAGES * STAGE_BYTES + STAGING_BYTES + EPI_WARPS * COLS_PER_WARP * 4 + 512 <= 232448;
+    static constexpr int BIAS_BYTES = BIAS_IN_SMEM ? EPI_WARPS * COLS_PER_WARP * 4 : 0;
     static constexpr int THREADS = (3 + EPI_WARPS) * 32;         // producer, MMA, epilogue warps, side-data loader
     static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STAGING_BYTES + BIAS_BYTES + BAR_BYTES;
     static_assert(STAGE_BYTES % 1024 == 0, "every operand tile must start on a swizzle-atom boundary");
@@ -239,9 +243,25 @@ struct EpiCtx {
 // bias16: the 16 fp32 bias values of these columns in shared memory (FC1 / FC2).  With side data
 // (patch-embed table, FC2 residual) the 16 bf16 side values already sit in the staging region at the
 // very place the result goes; they are read, combined and overwritten.
-template <int OP, int OUT, int H>
-__device__ __forceinline__ void epilogue_16(const float (&v)[32], const EpiCtx& e, const float* bias16, uint32_t region,
-                                            int piece0) {
+// Four consecutive bias values of the half-chunk: from the warp's shared copy, or (BSM false) from the chunk's
+// bias register of lanes first .. first + 3.  Every lane of the warp must call it.
+template <bool BSM>
+__device__ __forceinline__ float4 bias_quad(const float* bias16, float breg, int first, int i) {
+    if constexpr (BSM) {
+        return *reinterpret_cast<const float4*>(bias16 + 4 * i);
+    } else {
+        float4 b;
+        b.x = __shfl_sync(0xffffffffu, breg, first + 4 * i + 0);
+        b.y = __shfl_sync(0xffffffffu, breg, first + 4 * i + 1);
+        b.z = __shfl_sync(0xffffffffu, breg, first + 4 * i + 2);
+        b.w = __shfl_sync(0xffffffffu, breg, first + 4 * i + 3);
+        return b;
+    }
+}
+
+template <int OP, int OUT, int H, bool BSM>
+__device__ __forceinline__ void epilogue_16(const float (&v)[32], const EpiCtx& e, const float* bias16, float breg,
+                                            uint32_t region, int piece0) {
     float x[16];
     uint32_t w[8];  // bf16: 8 words (16 values); e4m3: 4 words used
     const uint32_t a0 = region + e.row_off + (((piece0 + 0) ^ e.swz) << 4);
@@ -269,7 +289,7 @@ __device__ __forceinline__ void epilogue_16(const float (&v)[32], const EpiCtx& 
         uint64_t g[8];
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            const float4 b = *reinterpret_cast<const float4*>(bias16 + 4 * i);
+            const float4 b = bias_quad<BSM>(bias16, breg, 16 * H, i);
             g[2 * i + 0] = fma_f32x2(pack_f32x2(v[16 * H + 4 * i + 0], v[16 * H + 4 * i + 1]), scale2, pack_f32x2(b.x, b.y));
             g[2 * i + 1] = fma_f32x2(pack_f32x2(v[16 * H + 4 * i + 2], v[16 * H + 4 * i + 3]), scale2, pack_f32x2(b.z, b.w));
         }
@@ -299,7 +319,7 @@ __device__ __forceinline__ void epilogue_16(const float (&v)[32], const EpiCtx& 
     } else {  // OP_FC2: (acc * scale + bias) + residual, fc2.cu:27-46
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            const float4 b = *reinterpret_cast<const float4*>(bias16 + 4 * i);
+            const float4 b = bias_quad<BSM>(bias16, breg, 16 * H, i);
             x[4 * i + 0] = fmaf(v[16 * H + 4 * i + 0], e.scale, b.x);
             x[4 * i + 1] = fmaf(v[16 * H + 4 * i + 1], e.scale, b.y);
             x[4 * i + 2] = fmaf(v[16 * H + 4 * i + 2], e.scale, b.z);
@@ -640,13 +660,19 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
         constexpr int NB = T::COLS_PER_WARP / 32;  // bias values each lane stages per tile
         float* const bias_w = reinterpret_cast<float*>(base_ptr + (bias_base - base)) + ew * T::COLS_PER_WARP;
-        float bnext[NB];
+        constexpr bool BSM = T::BIAS_IN_SMEM;
+        float bnext[NB], bcur[NB];
+#pragma unroll
+        for (int i = 0; i < NB; i++) bcur[i] = bnext[i] = 0.0f;
         if constexpr (HAS_BIAS) {
             if (cluster_id < p.num_tiles) {
                 const int tn0 = cluster_id % p.tiles_n;
                 load_bias<NB>(bnext, p.bias, p.flags, tn0 * TN + col_begin, lane, p.N);
 #pragma unroll
-                for (int i = 0; i < NB; i++) bias_w[lane + 32 * i] = bnext[i];
+                for (int i = 0; i < NB; i++) {
+                    if constexpr (BSM) bias_w[lane + 32 * i] = bnext[i];
+                    else bcur[i] = bnext[i];
+                }
                 __syncwarp();
             }
         }
@@ -731,8 +757,14 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                             if (prof) t0 = clock64();
                             const int piece0 = ch * 2 * T::OUT_BYTES;            // 32 columns = 2 (e4m3) or 4 (bf16) pieces
                             const float* bias32 = bias_w + (c - col_begin);
-                            epilogue_16<OP, OUT, 0>(v, e, bias32, region, piece0);
-                            if (n0 + c + 16 < p.N) epilogue_16<OP, OUT, 1>(v, e, bias32 + 16, region, piece0 + T::OUT_BYTES);
+                            float breg = bcur[0];                       // this chunk's bias, one column per lane
+                            if constexpr (!BSM) {
+#pragma unroll
+                                for (int i = 1; i < NB; i++)
+                                    if (i == r * T::CHUNKS_PER_REGION + ch) breg = bcur[i];
+                            }
+                            epilogue_16<OP, OUT, 0, BSM>(v, e, bias32, breg, region, piece0);
+                            if (n0 + c + 16 < p.N) epilogue_16<OP, OUT, 1, BSM>(v, e, bias32 + 16, breg, region, piece0 + T::OUT_BYTES);
                             if (prof) t_math += clock64() - t0;
                         }
                     }
@@ -773,7 +805,10 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 if (has_next) {
                     __syncwarp();                        // every lane has finished reading this tile's bias
 #pragma unroll
-                    for (int i = 0; i < NB; i++) bias_w[lane + 32 * i] = bnext[i];
+                    for (int i = 0; i < NB; i++) {
+                        if constexpr (BSM) bias_w[lane + 32 * i] = bnext[i];
+                        else bcur[i] = bnext[i];
+                    }
                     __syncwarp();
                 }
             }

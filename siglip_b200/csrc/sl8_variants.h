@@ -33,9 +33,10 @@
     X(11, 2, 256, 256, 2, 8, 2)  \
     X(12, 2, 256, 128, 3, 8, 3)  \
     X(13, 2, 256, 128, 4, 4, 3)  \
-    X(14, 2, 256, 128, 4, 16, 1)
+    X(14, 2, 256, 128, 4, 16, 1)  \
+    X(15, 2, 256, 128, 5, 16, 1)
 
-#define SL8_NUM_VARIANTS 15
+#define SL8_NUM_VARIANTS 16
 
 namespace sl8 {
 
