@@ -34,9 +34,10 @@
     X(12, 2, 256, 128, 3, 8, 3)  \
     X(13, 2, 256, 128, 4, 4, 3)  \
     X(14, 2, 256, 128, 4, 16, 1)  \
-    X(15, 2, 256, 128, 5, 16, 1)
+    X(15, 2, 256, 128, 5, 16, 1) \
+    X(16, 2, 256, 128, 6, 4, 2)
 
-#define SL8_NUM_VARIANTS 16
+#define SL8_NUM_VARIANTS 17
 
 namespace sl8 {
 
