@@ -39,7 +39,7 @@ UNIT = "TFLOP/s"
 # DRAM bytes per GEMM row of the dominant kernel, from one `ncu --set full` capture per configuration on a
 # smaller case (profiles/*_ncu.md: dram__bytes_read.sum + dram__bytes_write.sum divided by the rows of the
 # captured launch).  Traffic grows in proportion to the rows, so a full launch is this figure times M.
-NCU_DRAM_BYTES_PER_ROW = {"C2": 319.79e6 / 37908, "C3": 325.66e6 / 37908, "C4": 167.48e6 / 75816}
+NCU_DRAM_BYTES_PER_ROW = {"C2": 319.79e6 / 37908, "C3": 325.66e6 / 37908, "C4": 169.41e6 / 75816}
 
 
 # ----------------------------------------------------------------------------- peaks

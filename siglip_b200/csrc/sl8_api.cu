@@ -87,7 +87,7 @@ int pick_variant(int op, int out_dtype, long long M, int N, int K) {
     // fifth 256-wide tile half empty.
     if (op == SL8_OP_FC1_GELU)                // GELU epilogue: four epilogue warps per scheduler (bf16 out), else two
         return out_dtype == SL8_OUT_BF16 ? 15 : 2;
-    if (op == SL8_OP_PATCH_EMBED) return 5;   // short K: four staging boxes keep the table loads ahead of the epilogue
+    if (op == SL8_OP_PATCH_EMBED) return 17;  // short K: eight epilogue warps, three staging boxes per column group, four stages
     return 1;
 }
 

@@ -35,9 +35,10 @@
     X(13, 2, 256, 128, 4, 4, 3)  \
     X(14, 2, 256, 128, 4, 16, 1)  \
     X(15, 2, 256, 128, 5, 16, 1) \
-    X(16, 2, 256, 128, 6, 4, 2)
+    X(16, 2, 256, 128, 6, 4, 2)  \
+    X(17, 2, 256, 128, 4, 8, 3)
 
-#define SL8_NUM_VARIANTS 17
+#define SL8_NUM_VARIANTS 18
 
 namespace sl8 {
 

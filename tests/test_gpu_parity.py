@@ -174,7 +174,7 @@ def test_periodic_table_helpers(engine):
     assert torch.equal(engine.padded_table(want[:196].contiguous()), want)
 
 
-@pytest.mark.parametrize("vid", range(17))
+@pytest.mark.parametrize("vid", range(18))
 def test_every_variant(engine, oracle, vid):
     assert vid < num_variants()
     engine.set_variant(vid)
