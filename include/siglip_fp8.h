@@ -251,8 +251,9 @@ int sl8_fc2_residual_fp8_host(sl8_handle_t h,
 
 /* ---- dispatch ------------------------------------------------------------------------- */
 
-/* Variant the dispatch table selects for (op, out_dtype, M, N, K); the reference has a
- * single compile-time configuration (kernel_common.cuh:18-51,86-88). */
+/* Variant the dispatch table selects for (op, out_dtype, M, N, K) and flags = 0; the reference has a
+ * single compile-time configuration (kernel_common.cuh:18-51,86-88).  An FC1 call with SL8_FLAG_NO_ACTIVATION or
+ * SL8_FLAG_GELU_HW_TANH runs the eight-epilogue-warp variant where this answers with a sixteen-warp one. */
 int sl8_query_config(sl8_handle_t h, int op, int out_dtype, int64_t M, int N, int K, sl8_config* out);
 
 /* Number of compiled variants, and the description of variant `variant_id`. */
