@@ -115,6 +115,8 @@ def cpu_oracle_rate(cfg_name: str, target_seconds: float, seed: int = 0):
     from siglip_b200 import synth
     from tests.oracle_lib import Oracle
     orc = Oracle()
+    # torchrun exports OMP_NUM_THREADS=1 to its ranks; the CPU arm is meant to use every core this process may run on.
+    orc.lib.sl8o_set_num_threads(len(os.sched_getaffinity(0)))
     c = synth.CONFIGS[cfg_name]
     rows_per_image = c["M"] // c["images"]
 
@@ -503,7 +505,7 @@ def main() -> None:
             line["roofline"] = {"bound": "hbm", "achieved": per_gpu_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                 "frac": per_gpu_gbs / peaks["hbm_gbs"], "traffic": traffic,
                                 "peak_source": f"{peaks['source']} copy bandwidth", "tflops": per_gpu_tf}
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:      # a reported baseline of the one-GPU run only
             v, cores, sample, secs = cpu_oracle_rate(args.config, args.cpu_seconds)
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
                                     "seconds": secs}
