@@ -5,8 +5,8 @@ oracle/_ref/libsl8_ref_{pe,fc1,fc2}.so behind a small launch shim (oracle/ref_sh
 reference is shaped at compile time: M = 928 256 rows and its SigLIP-B/16 N, K, operands consumed as
 raw e4m3 codes (scale 1), fp32 bias, a 32x32-blocked bf16 bias+pos table.  Each test feeds both
 implementations the same random codes at exactly that shape, compares the outputs, arbitrates on a
-row sample with the CPU oracle, and records both kernels' times (CUDA events) in
-gpurun_out/ref_compare.txt when that directory exists.
+row sample with the CPU oracle, prints both kernels' times (CUDA events) and appends them to
+ref_compare.txt in the directory SL8_REPORT_DIR names, when it is set.
 
 The reference's own validation uses constant rows (every output row equal), so it cannot see a
 permutation of rows; these tests can.
@@ -69,10 +69,10 @@ def time_ms(fn, iters=10):
 
 
 def record(line):
-    out = ROOT / "gpurun_out"
     print(line)
-    if out.is_dir():
-        with open(out / "ref_compare.txt", "a") as f:
+    out = os.environ.get("SL8_REPORT_DIR")
+    if out and Path(out).is_dir():
+        with open(Path(out) / "ref_compare.txt", "a") as f:
             f.write(line + "\n")
 
 
