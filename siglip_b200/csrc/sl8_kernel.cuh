@@ -37,6 +37,10 @@
 
 #include "sl8_ptx.cuh"
 
+#ifndef SL8_SPIN_CRITICAL
+#define SL8_SPIN_CRITICAL true
+#endif
+
 namespace sl8 {
 
 enum : int { OP_PE = 0, OP_FC1 = 1, OP_FC2 = 2 };
@@ -159,13 +163,16 @@ struct WaitCtx {
 
 // Polls `bar` until the phase with parity `parity` has completed.  Returns false if the CTA
 // is aborting or the budget ran out (in which case it records `code` and raises the flag).
+// SPIN: poll without parking the thread (the two single-thread roles on the critical path, whose wake-up
+// latency is paid by the whole CTA pair); otherwise each poll may park the thread until the phase completes.
+template <bool SPIN = false>
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, const WaitCtx& w, uint32_t code,
                                          uint32_t which) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (SPIN ? (mbar_test_wait(bar, parity) != 0u) : mbar_try_wait(bar, parity)) return true;
     unsigned long long t0 = 0;
     for (uint32_t spins = 1;; ++spins) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((spins & 15u) == 0) {   // each poll may have been parked for up to 20 us
+        if (SPIN ? (mbar_test_wait(bar, parity) != 0u) : mbar_try_wait(bar, parity)) return true;
+        if ((spins & (SPIN ? 255u : 15u)) == 0) {   // each parked poll may have lasted up to 20 us
             if (*w.abort_flag) return false;
             const unsigned long long now = globaltimer_ns();
             if (t0 == 0) {
@@ -452,7 +459,7 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const int nb = tn * TN + static_cast<int>(cta_rank) * T::B_ROWS;
                 for (int kb = 0; kb < p.k_blocks; kb++) {
                     const long long t0 = prof ? clock64() : 0;
-                    ok = wait_bar(empty_bar0 + 8 * stage, phase ^ 1u, wc, ST_PRODUCER_EMPTY_WAIT, stage);
+                    ok = wait_bar<SL8_SPIN_CRITICAL>(empty_bar0 + 8 * stage, phase ^ 1u, wc, ST_PRODUCER_EMPTY_WAIT, stage);
                     if (prof) t_wait += clock64() - t0;
                     if (!ok) break;
                     const uint32_t a_dst = base + stage * T::STAGE_BYTES;
@@ -538,7 +545,7 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             for (int tile = cluster_id; ok && tile < p.num_tiles; tile += num_clusters) {
                 wc.tile = tile;
                 long long t0 = prof ? clock64() : 0;
-                ok = wait_bar(tempty_bar0 + 8 * acc, acc_phase ^ 1u, wc, ST_MMA_TMEM_EMPTY_WAIT, acc);
+                ok = wait_bar<SL8_SPIN_CRITICAL>(tempty_bar0 + 8 * acc, acc_phase ^ 1u, wc, ST_MMA_TMEM_EMPTY_WAIT, acc);
                 if (prof) t_tmem += clock64() - t0;
                 n_tiles++;
                 if (!ok) break;
@@ -550,7 +557,7 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     // One k-block: wait (only if the look-ahead failed), look ahead, MMAs, release the stage.
                     // n < 4 * KATOMS only in the K tail.
                     auto step = [&](bool fresh, int n) -> bool {
-                        if (!ready && !wait_bar(full_bar0 + 8 * stage, phase, wc, ST_MMA_FULL_WAIT, stage)) return false;
+                        if (!ready && !wait_bar<SL8_SPIN_CRITICAL>(full_bar0 + 8 * stage, phase, wc, ST_MMA_FULL_WAIT, stage)) return false;
                         const int s1 = (stage + 1 == STAGES) ? 0 : stage + 1;
                         const uint32_t ph1 = (s1 == 0) ? (phase ^ 1u) : phase;
                         const uint32_t r1 = mbar_test_wait(full_bar0 + 8 * s1, ph1);
@@ -589,7 +596,7 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 }
                 for (; kb < p.k_blocks; kb++) {
                     if (prof) t0 = clock64();
-                    if (!ready) ok = wait_bar(full_bar0 + 8 * stage, phase, wc, ST_MMA_FULL_WAIT, stage);
+                    if (!ready) ok = wait_bar<SL8_SPIN_CRITICAL>(full_bar0 + 8 * stage, phase, wc, ST_MMA_FULL_WAIT, stage);
                     if (prof) t_full += clock64() - t0;
                     if (!ok) break;
                     const int s1 = (stage + 1 == STAGES) ? 0 : stage + 1;
