@@ -56,7 +56,7 @@ enum : int { OUT_BF16 = 0, OUT_E4M3 = 1 };
 enum : unsigned { FLAG_BIAS_F32 = 1u, FLAG_PE_F32_ADD = 2u, FLAG_NO_ACTIVATION = 4u, FLAG_GELU_HW_TANH = 8u,
                   DBG_SKIP_SIDE = 0x100u, DBG_SKIP_GELU = 0x200u, DBG_SKIP_BIAS = 0x400u, DBG_SKIP_STORE = 0x800u,
                   DBG_SKIP_LOAD = 0x1000u, DBG_SKIP_EPILOGUE = 0x2000u, DBG_SKIP_MMA = 0x4000u,
-                  DBG_SKIP_A = 0x8000u, DBG_SKIP_B = 0x10000u,
+                  DBG_SKIP_A = 0x8000u, DBG_SKIP_B = 0x10000u, DBG_SKIP_TMEM_LD = 0x20000u, DBG_SKIP_MATH = 0x40000u,
                   DBG_COARSE_TRACE = 0x80000000u };   // record per-role totals only (the inner timers cost ~35 cycles each)
 
 // status[0] codes: which role gave up.
@@ -747,9 +747,14 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         const int c = c0 + 32 * ch;
                         if (n0 + c < p.N) {
                             float v[32];
-                            tmem_ld_32x32(t_row + c, v);
+                            if (SL8_DBG(p.flags, DBG_SKIP_TMEM_LD)) {   // measurement aid: the epilogue works on constants
+#pragma unroll
+                                for (int i = 0; i < 32; i++) v[i] = 1.0f;
+                            } else {
+                                tmem_ld_32x32(t_row + c, v);
+                            }
                             if (prof) t0 = clock64();
-                            tmem_ld_wait();
+                            if (!SL8_DBG(p.flags, DBG_SKIP_TMEM_LD)) tmem_ld_wait();
                             if (prof) t_ld += clock64() - t0;
                             if (r == RPT - 1 && ch == T::CHUNKS_PER_REGION - 1) {
                                 // Last read of this accumulator: hand the TMEM buffer back before the math.
@@ -770,8 +775,10 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                 for (int i = 1; i < NB; i++)
                                     if (i == r * T::CHUNKS_PER_REGION + ch) breg = bcur[i];
                             }
-                            epilogue_16<OP, OUT, 0, BSM>(v, e, bias32, breg, region, piece0);
-                            if (n0 + c + 16 < p.N) epilogue_16<OP, OUT, 1, BSM>(v, e, bias32 + 16, breg, region, piece0 + T::OUT_BYTES);
+                            if (!SL8_DBG(p.flags, DBG_SKIP_MATH)) {
+                                epilogue_16<OP, OUT, 0, BSM>(v, e, bias32, breg, region, piece0);
+                                if (n0 + c + 16 < p.N) epilogue_16<OP, OUT, 1, BSM>(v, e, bias32 + 16, breg, region, piece0 + T::OUT_BYTES);
+                            }
                             if (prof) t_math += clock64() - t0;
                         }
                     }
