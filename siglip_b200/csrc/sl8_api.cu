@@ -98,8 +98,7 @@ int pick_variant_exact_gelu(int op, int out_dtype, long long M, int N, int K) {
     // A tcgen05.mma of a CTA pair takes about 150 cycles whatever its N (measured for N = 128, 192,
     // 256), so the widest tile does the most work per instruction even where N = 1152 leaves the
     // fifth 256-wide tile half empty.
-    if (op == SL8_OP_FC1_GELU)                // GELU epilogue: four epilogue warps per scheduler (bf16 out), else two
-        return out_dtype == SL8_OUT_BF16 ? 15 : 2;
+    if (op == SL8_OP_FC1_GELU) return 15;     // GELU epilogue: four epilogue warps per scheduler
     if (op == SL8_OP_PATCH_EMBED) return 17;  // short K: eight epilogue warps, three staging boxes per column group, four stages
     return 1;
 }
@@ -167,11 +166,11 @@ int validate(sl8_handle_t h, const Problem& q) {
 
 int encode_2d(sl8_handle_t h, CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* base,
               unsigned long long inner, unsigned long long outer, unsigned long long pitch_bytes, unsigned box_inner,
-              unsigned box_outer, CUtensorMapL2promotion promo) {
+              unsigned box_outer, CUtensorMapL2promotion promo, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
     for (int i = 0; i < sl8_context::kMapCache; i++) {      // callers hold h->mu
         const MapCacheEntry& c = h->map_cache[i];
         if (c.base == base && c.dt == (int)dt && c.promo == (int)promo && c.inner == inner && c.outer == outer &&
-            c.pitch == pitch_bytes && c.box_inner == box_inner && c.box_outer == box_outer) {
+            c.pitch == pitch_bytes && c.box_inner == box_inner && c.box_outer == box_outer && c.swizzle == (int)swizzle) {
             *map = c.map;
             return SL8_OK;
         }
@@ -182,12 +181,12 @@ int encode_2d(sl8_handle_t h, CUtensorMap* map, CUtensorMapDataType dt, int elem
     cuuint32_t estr[2] = {1, 1};
     (void)elem_bytes;
     CUresult r = h->encode(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                           CU_TENSOR_MAP_SWIZZLE_128B, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                           swizzle, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r == CUDA_SUCCESS) {
         MapCacheEntry& c = h->map_cache[h->map_cache_next];
         h->map_cache_next = (h->map_cache_next + 1) % sl8_context::kMapCache;
         c.dt = (int)dt; c.promo = (int)promo; c.base = base; c.inner = inner; c.outer = outer; c.pitch = pitch_bytes;
-        c.box_inner = box_inner; c.box_outer = box_outer; c.map = *map;
+        c.box_inner = box_inner; c.box_outer = box_outer; c.swizzle = (int)swizzle; c.map = *map;
     }
     if (r != CUDA_SUCCESS) {
         char buf[160];
@@ -252,9 +251,12 @@ int run(sl8_handle_t h, const Problem& q, cudaStream_t stream) {
     rc = encode_2d(h, &map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q.B, (unsigned long long)q.K, (unsigned long long)q.N,
                    (unsigned long long)q.ldb, 128, (unsigned)(v->tn / v->cg), CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
     if (rc != SL8_OK) return rc;
+    // Staging rows (= store boxes) are 128 bytes wide, 64 where one epilogue warp's columns fill no more.
+    const int row_bytes = (v->tn / (v->epi_warps / 4)) * ob < 128 ? 64 : 128;
     rc = encode_2d(h, &map_d, ob == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, ob, q.D,
                    (unsigned long long)q.N, (unsigned long long)q.M, (unsigned long long)q.ldd * ob,
-                   (unsigned)(128 / ob), 32, CU_TENSOR_MAP_L2_PROMOTION_NONE);
+                   (unsigned)(row_bytes / ob), 32, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                   row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
     if (rc != SL8_OK) return rc;
 
     // Side data (table [period, N] or residual [M, N], bf16) comes in by TMA as 128-row x 64-column boxes.

@@ -38,7 +38,7 @@ struct Sl8HostPipe {
 // Tensor maps of recent calls, keyed by everything that goes into one: a layer called again on the same buffers
 // (every step of a model) skips the four driver encodes, which cost more host time than the launch itself.
 struct Sl8MapCacheEntry {
-    int dt = -1, promo = 0;
+    int dt = -1, promo = 0, swizzle = 0;
     const void* base = nullptr;
     unsigned long long inner = 0, outer = 0, pitch = 0;
     unsigned box_inner = 0, box_outer = 0;

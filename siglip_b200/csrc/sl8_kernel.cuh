@@ -135,10 +135,13 @@ struct KernelTraits {
     static constexpr int ACC_STRIDE = TN;                        // TMEM columns between the two accumulators
     static constexpr int TMEM_COLS = 2 * TN;                     // 256 or 512: a power of two >= 32
     static constexpr int OUT_BYTES = (OUT == OUT_BF16) ? 2 : 1;
-    static constexpr int REGION_COLS = 128 / OUT_BYTES;          // output columns in one 128-byte staging row
-    static constexpr int REGION_BYTES = 32 * 128;                // 32 rows of one warp
-    static constexpr int STAGING_BYTES = EPI_WARPS * NBUF * REGION_BYTES;
     static constexpr int COLS_PER_WARP = TN / (EPI_WARPS / 4);   // columns one epilogue warp covers
+    // A staging row is 128 bytes (SWIZZLE_128B), or 64 (SWIZZLE_64B) where a warp's columns fill no more: e4m3
+    // output from sixteen epilogue warps, 64 one-byte columns each.
+    static constexpr int REGION_ROW_BYTES = (COLS_PER_WARP * OUT_BYTES < 128) ? 64 : 128;
+    static constexpr int REGION_COLS = REGION_ROW_BYTES / OUT_BYTES;   // output columns in one staging row
+    static constexpr int REGION_BYTES = 32 * REGION_ROW_BYTES;   // 32 rows of one warp
+    static constexpr int STAGING_BYTES = EPI_WARPS * NBUF * REGION_BYTES;
     static constexpr int REGIONS_PER_TILE = COLS_PER_WARP / REGION_COLS;
     static constexpr int CHUNKS_PER_REGION = REGION_COLS / 32;   // 32-column tcgen05.ld chunks per region
     static constexpr int BAR_BYTES = 512;                        // pipeline barriers + two per staging box
@@ -240,8 +243,8 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, ui
 struct EpiCtx {
     float scale;      // scale_a * scale_b
     float inv_out;    // 1 / out_scale
-    uint32_t row_off; // lane * 128: byte offset of this lane's row inside a staging region
-    uint32_t swz;     // lane & 7: XOR applied to the 16-byte piece index (SWIZZLE_128B)
+    uint32_t row_off; // lane * row bytes: byte offset of this lane's row inside a staging region
+    uint32_t swz;     // XOR applied to the 16-byte piece index: lane & 7 (SWIZZLE_128B) or (lane >> 1) & 3 (SWIZZLE_64B)
     unsigned flags;
 };
 
@@ -655,8 +658,8 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         e.scale = (p.scale_a ? __ldg(p.scale_a) : 1.0f) * (p.scale_b ? __ldg(p.scale_b) : 1.0f);
         e.inv_out = __frcp_rn(p.out_scale ? __ldg(p.out_scale) : 1.0f);   // IEEE 1/x, as the CPU oracle computes it
         e.flags = p.flags;
-        e.swz = lane & 7;
-        e.row_off = lane * 128;
+        e.swz = (T::REGION_ROW_BYTES == 128) ? (lane & 7) : ((lane >> 1) & 3);
+        e.row_off = lane * T::REGION_ROW_BYTES;
         // Staging is organised per column group (the four quadrant warps that cover the same columns):
         // NBUF boxes of 128 rows x 128 bytes, of which this warp owns rows 32 * quad .. 32 * quad + 31.
         const uint32_t my_staging = staging_base + col_part * NBUF * 4 * T::REGION_BYTES + quad * T::REGION_BYTES;

@@ -47,7 +47,7 @@ template <int ID, int CG, int TN, int TK, int STAGES, int EW, int NBUF>
 const VariantEntry* make_entry() {
     constexpr bool SIDE = NBUF >= 2;   // layers with side data need a second staging buffer
     using T16 = KernelTraits<CG, TN, TK, STAGES, EW, OUT_BF16, NBUF>;
-    constexpr bool E4 = (TN / (EW / 4)) % 128 == 0;   // an e4m3 staging region is 128 columns wide
+    constexpr bool E4 = (TN / (EW / 4)) % 64 == 0;   // an e4m3 staging region is 128 or 64 columns wide
     using T8 = std::conditional_t<E4, KernelTraits<CG, TN, TK, STAGES, EW, E4 ? OUT_E4M3 : OUT_BF16, NBUF>, T16>;
     static const VariantEntry e = {
         ID, CG, TN, TK, STAGES, EW, NBUF, T16::THREADS,
