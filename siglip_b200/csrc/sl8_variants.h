@@ -14,7 +14,8 @@
 //   TK         bytes of K per pipeline stage: 128 or 256 (one or two swizzle atoms; with 256 the
 //              MMA thread issues eight MMAs per barrier round trip instead of four)
 //   STAGES     depth of the operand ring (bounded by the 227 KiB of shared memory)
-//   EPI_WARPS  4 = one warp per TMEM lane quadrant, 8 = two (each takes half the columns)
+//   EPI_WARPS  4 = one warp per TMEM lane quadrant, 8 = two (each takes half the columns), 16 = four (a quarter each;
+//              e4m3 output then goes through 64-byte staging rows)
 //   NBUF       staging buffers (32 rows x 128 bytes) per epilogue warp.  The layers with side data
 //              (patch-embed table, FC2 residual) prefetch it NBUF - 1 regions ahead and need
 //              NBUF >= 2; a variant with NBUF = 1 serves FC1 only.
