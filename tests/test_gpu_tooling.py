@@ -43,4 +43,4 @@ def test_dispatch_answers_from_the_committed_table(engine):
         assert engine.query_config(r["op"], m, r["N"], r["K"])["variant_id"] == r["variant"], r
     # a shape the sweep does not hold falls back to the rules
     assert engine.query_config(1, 50000, 2048, 1024)["variant_id"] == 15
-    assert engine.query_config(1, 50000, 2048, 1024, out_dtype=1)["variant_id"] == 2      # e4m3 out: sixteen warps have no kernel
+    assert engine.query_config(1, 50000, 2048, 1024, out_dtype=1)["variant_id"] == 15     # e4m3 out: sixteen warps, 64-byte staging rows
