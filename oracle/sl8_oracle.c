@@ -33,6 +33,7 @@
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
+#include <immintrin.h>
 #ifdef _OPENMP
 #include <omp.h>
 #endif
@@ -160,6 +161,10 @@ SL8O_API void sl8o_dequantize_e4m3(const uint8_t* c, int64_t n, float* out) {
 /* ------------------------------------------------------------------ GEMM */
 
 typedef float v8f __attribute__((vector_size(32)));
+/* acc += a * b on eight lanes as one fused multiply-add.  The product of two e4m3 values has at most eight significant
+ * bits, so it is exact in FP32 and the fused form rounds exactly as a separate multiply and add would: the instruction
+ * is chosen for speed (this GEMM is also the timed CPU baseline), not for its rounding. */
+#define FMA8(acc, a, b) ((acc) = (v8f)_mm256_fmadd_ps((__m256)(a), (__m256)(b), (__m256)(acc)))
 
 static inline float hsum8(v8f v) {
     return ((v[0] + v[4]) + (v[1] + v[5])) + ((v[2] + v[6]) + (v[3] + v[7]));
@@ -207,10 +212,10 @@ SL8O_API int sl8o_gemm_fp8_f32(const uint8_t* A, int64_t lda, const uint8_t* B, 
                     v8f c00 = {0}, c01 = {0}, c10 = {0}, c11 = {0}, c20 = {0}, c21 = {0}, c30 = {0}, c31 = {0};
                     for (int k = 0; k < Kp; k += 8) {
                         v8f vb0 = *(const v8f*)(b0 + k), vb1 = *(const v8f*)(b1 + k);
-                        v8f va = *(const v8f*)(a0 + k); c00 += va * vb0; c01 += va * vb1;
-                        va = *(const v8f*)(a1 + k);     c10 += va * vb0; c11 += va * vb1;
-                        va = *(const v8f*)(a2 + k);     c20 += va * vb0; c21 += va * vb1;
-                        va = *(const v8f*)(a3 + k);     c30 += va * vb0; c31 += va * vb1;
+                        v8f va = *(const v8f*)(a0 + k); FMA8(c00, va, vb0); FMA8(c01, va, vb1);
+                        va = *(const v8f*)(a1 + k);     FMA8(c10, va, vb0); FMA8(c11, va, vb1);
+                        va = *(const v8f*)(a2 + k);     FMA8(c20, va, vb0); FMA8(c21, va, vb1);
+                        va = *(const v8f*)(a3 + k);     FMA8(c30, va, vb0); FMA8(c31, va, vb1);
                     }
                     float* o = acc + m * ldacc + n;
                     o[0] = hsum8(c00); o[1] = hsum8(c01); o += ldacc;
@@ -223,8 +228,8 @@ SL8O_API int sl8o_gemm_fp8_f32(const uint8_t* A, int64_t lda, const uint8_t* B, 
                     v8f c0 = {0}, c1 = {0}, c2 = {0}, c3 = {0};
                     for (int k = 0; k < Kp; k += 8) {
                         v8f vb = *(const v8f*)(b0 + k);
-                        c0 += *(const v8f*)(a0 + k) * vb; c1 += *(const v8f*)(a1 + k) * vb;
-                        c2 += *(const v8f*)(a2 + k) * vb; c3 += *(const v8f*)(a3 + k) * vb;
+                        FMA8(c0, *(const v8f*)(a0 + k), vb); FMA8(c1, *(const v8f*)(a1 + k), vb);
+                        FMA8(c2, *(const v8f*)(a2 + k), vb); FMA8(c3, *(const v8f*)(a3 + k), vb);
                     }
                     acc[(m + 0) * ldacc + n] = hsum8(c0); acc[(m + 1) * ldacc + n] = hsum8(c1);
                     acc[(m + 2) * ldacc + n] = hsum8(c2); acc[(m + 3) * ldacc + n] = hsum8(c3);
@@ -235,7 +240,7 @@ SL8O_API int sl8o_gemm_fp8_f32(const uint8_t* A, int64_t lda, const uint8_t* B, 
                 for (int n = n0; n < n1; n++) {
                     const float* b0 = Bf + (int64_t)n * Kp;
                     v8f c0 = {0};
-                    for (int k = 0; k < Kp; k += 8) c0 += *(const v8f*)(a0 + k) * *(const v8f*)(b0 + k);
+                    for (int k = 0; k < Kp; k += 8) FMA8(c0, *(const v8f*)(a0 + k), *(const v8f*)(b0 + k));
                     acc[m * ldacc + n] = hsum8(c0);
                 }
             }
@@ -303,7 +308,7 @@ SL8O_API int sl8o_fc1_gelu(const uint8_t* A, int64_t lda, const uint8_t* B, int6
         for (int64_t i = 0; i < rows; i++) {
             const int64_t m = r0 + i;
             for (int n = 0; n < N; n++) {
-                const float x = acc[i * N + n] * s + bias_at(bias, n, flags);
+                const float x = fmaf(acc[i * N + n], s, bias_at(bias, n, flags));    /* one rounding, as the kernel's FMA */
                 const float g = (flags & 4u) ? x : sl8o_gelu_tanh(x);   /* fc1_gelu.cu:16-19; flag 4: no activation */
                 if (out_dtype == 0) ((uint16_t*)D)[m * ldd + n] = sl8o_f32_to_bf16(g);
                 else ((uint8_t*)D)[m * ldd + n] = sl8o_f32_to_e4m3(g * inv_out);
@@ -328,7 +333,7 @@ SL8O_API int sl8o_fc2_residual(const uint8_t* A, int64_t lda, const uint8_t* B, 
         for (int64_t i = 0; i < rows; i++) {
             const int64_t m = r0 + i;
             for (int n = 0; n < N; n++) {
-                float t = acc[i * N + n] * s + bias_at(bias, n, flags);            /* fc2.cu:27-30 */
+                float t = fmaf(acc[i * N + n], s, bias_at(bias, n, flags));          /* fc2.cu:27-30; one rounding, as the kernel's FMA */
                 t = t + sl8o_bf16_to_f32(residual[m * ldr + n]);                    /* fc2.cu:31-46 */
                 D[m * ldd + n] = sl8o_f32_to_bf16(t);                               /* fc2.cu:47-50 */
             }

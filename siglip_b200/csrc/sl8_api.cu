@@ -501,6 +501,9 @@ int run_host(sl8_handle_t h, Problem q, float scale_a, float scale_b, float out_
     if (q.op == SL8_OP_PATCH_EMBED && (!q.side || q.period < 1 || q.table_rows < q.period || q.ld_side < q.N || (q.ld_side * 2) % 16 || q.row_phase < 0))
         return fail(h, SL8_ERR_INVALID_VALUE, "bad table");
 
+    // One host call at a time per handle: the staging buffers and the three streams belong to the call that runs.
+    // (run() takes h->mu for the launch itself, so this is a second, outer lock.)
+    std::lock_guard<std::mutex> pipe_lock(h->pipe_mu);
     DeviceGuard guard(h->device);
     if (!guard.ok) return fail(h, SL8_ERR_CUDA, "cudaSetDevice failed");
     HostPipe& pp = h->pipe;
@@ -532,15 +535,23 @@ int run_host(sl8_handle_t h, Problem q, float scale_a, float scale_b, float out_
     if (q.bias && (rc = ensure(h, &pp.d_bias, &pp.bias_bytes, bias_need)) != SL8_OK) return rc;
     if (q.op == SL8_OP_PATCH_EMBED && (rc = ensure(h, &pp.d_table, &pp.table_bytes, (size_t)q.table_rows * q.ld_side * 2)) != SL8_OK) return rc;
 
+    // A copy or wait that cannot be enqueued ends the call: what was enqueued before it is drained first, so no
+    // copy is still writing into the caller's buffers when the error is returned.
+    auto bail = [&](cudaError_t err, const char* what) {
+        cudaDeviceSynchronize();
+        (void)cudaGetLastError();
+        return fail_cuda(h, err, what);
+    };
     // constants, once per call, on slot 0's stream
     cudaStream_t s0 = pp.stream[0];
     pp.h_scales[0] = scale_a; pp.h_scales[1] = scale_b; pp.h_scales[2] = out_scale;
-    cudaMemcpyAsync(pp.d_scales, pp.h_scales, 12, cudaMemcpyHostToDevice, s0);
-    cudaMemcpyAsync(pp.d_b, q.B, (size_t)q.N * q.ldb, cudaMemcpyHostToDevice, s0);
-    if (q.bias) cudaMemcpyAsync(pp.d_bias, q.bias, bias_need, cudaMemcpyHostToDevice, s0);
-    if (q.op == SL8_OP_PATCH_EMBED) cudaMemcpyAsync(pp.d_table, q.side, (size_t)q.table_rows * q.ld_side * 2, cudaMemcpyHostToDevice, s0);
-    e = cudaEventRecord(pp.consts_ready, s0);
-    if (e != cudaSuccess) return fail_cuda(h, e, "upload of constants");
+    if ((e = cudaMemcpyAsync(pp.d_scales, pp.h_scales, 12, cudaMemcpyHostToDevice, s0)) != cudaSuccess) return bail(e, "upload of the scales");
+    if ((e = cudaMemcpyAsync(pp.d_b, q.B, (size_t)q.N * q.ldb, cudaMemcpyHostToDevice, s0)) != cudaSuccess) return bail(e, "upload of B");
+    if (q.bias && (e = cudaMemcpyAsync(pp.d_bias, q.bias, bias_need, cudaMemcpyHostToDevice, s0)) != cudaSuccess) return bail(e, "upload of the bias");
+    if (q.op == SL8_OP_PATCH_EMBED &&
+        (e = cudaMemcpyAsync(pp.d_table, q.side, (size_t)q.table_rows * q.ld_side * 2, cudaMemcpyHostToDevice, s0)) != cudaSuccess)
+        return bail(e, "upload of the table");
+    if ((e = cudaEventRecord(pp.consts_ready, s0)) != cudaSuccess) return bail(e, "upload of constants");
 
     const uint8_t* hA = static_cast<const uint8_t*>(q.A);
     const uint8_t* hR = static_cast<const uint8_t*>(q.side);
@@ -549,9 +560,11 @@ int run_host(sl8_handle_t h, Problem q, float scale_a, float scale_b, float out_
     for (long long r0 = 0; r0 < q.M; r0 += slab, slot = (slot + 1) % HostPipe::SLOTS) {
         const long long rows = (r0 + slab < q.M) ? slab : q.M - r0;
         cudaStream_t s = pp.stream[slot];
-        if (slot != 0 || r0 == 0) cudaStreamWaitEvent(s, pp.consts_ready, 0);
-        cudaMemcpyAsync(pp.d_a[slot], hA + (size_t)r0 * q.lda, (size_t)rows * q.lda, cudaMemcpyHostToDevice, s);
-        if (has_res) cudaMemcpyAsync(pp.d_r[slot], hR + (size_t)r0 * q.ld_side * 2, (size_t)rows * q.ld_side * 2, cudaMemcpyHostToDevice, s);
+        if ((slot != 0 || r0 == 0) && (e = cudaStreamWaitEvent(s, pp.consts_ready, 0)) != cudaSuccess) return bail(e, "wait for the constants");
+        if ((e = cudaMemcpyAsync(pp.d_a[slot], hA + (size_t)r0 * q.lda, (size_t)rows * q.lda, cudaMemcpyHostToDevice, s)) != cudaSuccess)
+            return bail(e, "upload of a slab of A");
+        if (has_res && (e = cudaMemcpyAsync(pp.d_r[slot], hR + (size_t)r0 * q.ld_side * 2, (size_t)rows * q.ld_side * 2, cudaMemcpyHostToDevice, s)) != cudaSuccess)
+            return bail(e, "upload of a slab of the residual");
         Problem d = q;
         d.A = pp.d_a[slot];
         d.B = pp.d_b;
@@ -563,7 +576,8 @@ int run_host(sl8_handle_t h, Problem q, float scale_a, float scale_b, float out_
         if (has_res) d.side = pp.d_r[slot];
         rc = run(h, d, s);
         if (rc != SL8_OK) { cudaDeviceSynchronize(); return rc; }
-        cudaMemcpyAsync(hD + (size_t)r0 * q.ldd * ob, pp.d_d[slot], (size_t)rows * q.ldd * ob, cudaMemcpyDeviceToHost, s);
+        if ((e = cudaMemcpyAsync(hD + (size_t)r0 * q.ldd * ob, pp.d_d[slot], (size_t)rows * q.ldd * ob, cudaMemcpyDeviceToHost, s)) != cudaSuccess)
+            return bail(e, "download of a slab of D");
     }
     for (int i = 0; i < HostPipe::SLOTS; i++) {
         e = cudaStreamSynchronize(pp.stream[i]);
@@ -658,8 +672,10 @@ SL8_API int sl8_device_status(sl8_handle_t h, sl8_stream_t stream, unsigned deta
     char buf[160];
     static const char* names[] = {"", "producer waiting for a free stage", "MMA thread waiting for operands",
                                   "MMA thread waiting for a free accumulator", "epilogue waiting for an accumulator",
-                                  "epilogue waiting for table / residual data"};
-    snprintf(buf, sizeof buf, "device wait expired: %s (index %u, tile %u, block %u)", st[0] < 6 ? names[st[0]] : "?", st[1],
+                                  "epilogue waiting for table / residual data",
+                                  "table / residual loader waiting for a free staging box"};
+    constexpr unsigned kNames = sizeof names / sizeof names[0];
+    snprintf(buf, sizeof buf, "device wait expired: %s (index %u, tile %u, block %u)", st[0] < kNames ? names[st[0]] : "?", st[1],
              st[2], st[3]);
     return fail(h, SL8_ERR_DEVICE_TIMEOUT, buf);
 }

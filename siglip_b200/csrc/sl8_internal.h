@@ -61,7 +61,8 @@ struct sl8_context {
     unsigned wait_budget_ms = 2000;
     bool smem_attr_set[SL8_NUM_VARIANTS][sl8::K_COUNT] = {};
     int max_clusters[SL8_NUM_VARIANTS][sl8::K_COUNT] = {};
-    std::mutex mu;
+    std::mutex mu;          // the handle's state during one launch (map cache, attributes, error text)
+    std::mutex pipe_mu;     // the host-operand pipeline during one *_host call (taken before mu)
     std::string err;
     Sl8HostPipe pipe;
 };

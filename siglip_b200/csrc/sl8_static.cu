@@ -138,6 +138,9 @@ SL8_API int sl8_fc1_gelu_fp8_static(const void* A, int64_t lda, const void* B, i
     const int ob = out_dtype == SL8_OUT_BF16 ? 2 : 1;
     if (!aligned16(A) || !aligned16(B) || !aligned16(D) || (bias && !aligned16(bias)) || lda % 16 || ldb % 16 || (ldd * ob) % 16)
         return SL8_ERR_ALIGNMENT;
+    // The epilogue reads each scale with one 4-byte load: a misaligned pointer would fault on the device.
+    for (const float* sc : {scale_a, scale_b, out_scale})
+        if (sc && (reinterpret_cast<uintptr_t>(sc) & 3u)) return SL8_ERR_ALIGNMENT;
 
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess) return SL8_ERR_NO_DEVICE;
@@ -190,13 +193,16 @@ SL8_API int sl8_fc1_gelu_fp8_static(const void* A, int64_t lda, const void* B, i
     p.prof = host_trace ? reinterpret_cast<long long*>(s->scratch + kTraceOffset) : nullptr;
 
     // The array still holds the previous call's status: it has to start at zero.
-    if (cudaMemsetAsync(s->scratch, 0, 16, stream) != cudaSuccess) return SL8_ERR_CUDA;
+    if (cudaMemsetAsync(s->scratch, 0, 16, stream) != cudaSuccess) { (void)cudaGetLastError(); return SL8_ERR_CUDA; }
     if (v->launch[slot](&map_a, &map_b, &map_d, &map_d, &p, grid, stream) != cudaSuccess) {
         (void)cudaGetLastError();
         return SL8_ERR_CUDA;
     }
-    if (host_status && cudaMemcpyAsync(host_status, s->scratch, 16, cudaMemcpyDeviceToHost, stream) != cudaSuccess) return SL8_ERR_CUDA;
+    // From here on the kernel IS enqueued.  If one of the two read-back copies cannot be enqueued the call still
+    // reports the launch (the grid size): D will be written; only host_status / host_trace stay as they were, which
+    // the caller can tell from the sentinel it put there (the copies never leave word 0 of host_status at 0xFFFFFFFF).
+    if (host_status && cudaMemcpyAsync(host_status, s->scratch, 16, cudaMemcpyDeviceToHost, stream) != cudaSuccess) (void)cudaGetLastError();
     if (host_trace && cudaMemcpyAsync(host_trace, s->scratch + kTraceOffset, static_cast<size_t>(grid) * SL8_TRACE_SLOTS * 8,
-                                      cudaMemcpyDeviceToHost, stream) != cudaSuccess) return SL8_ERR_CUDA;
+                                      cudaMemcpyDeviceToHost, stream) != cudaSuccess) (void)cudaGetLastError();
     return grid;   // > 0: CTAs launched = trace records that will arrive in host_trace
 }

@@ -70,6 +70,8 @@ class Engine:
             raise ValueError("A [M, K] and B [N, K] must be 2-D with K contiguous")
         if not (A.is_cuda and B.is_cuda):
             raise ValueError("A and B must be CUDA tensors (use the *_host methods for host operands)")
+        self._on_device("A", A)
+        self._on_device("B", B)
         M, K = A.shape
         N, Kb = B.shape
         if K != Kb:
@@ -79,6 +81,46 @@ class Engine:
     @staticmethod
     def _new_out(M: int, N: int, dtype: torch.dtype, device) -> torch.Tensor:
         return torch.empty((M, N), dtype=dtype, device=device)
+
+    def _on_device(self, name: str, t: Optional[torch.Tensor]) -> None:
+        """Every device operand must live on the GPU this handle is bound to: the library dereferences
+        the pointer on that GPU whatever device the tensor says it is on."""
+        if t is None:
+            return
+        if not t.is_cuda:
+            raise ValueError(f"{name} must be a CUDA tensor")
+        if t.device.index != self.device:
+            raise ValueError(f"{name} is on cuda:{t.device.index}, this engine is bound to cuda:{self.device}")
+
+    def _check_out(self, out: torch.Tensor, M: int, N: int, allowed: tuple) -> torch.Tensor:
+        """A caller-supplied output: [M, N], N contiguous, on this engine's GPU, of an element type the
+        layer can write.  The kernel's output type is then taken from the tensor, never from a keyword."""
+        if out.dtype not in allowed:
+            raise TypeError(f"out has dtype {out.dtype}; this layer writes {' / '.join(str(a) for a in allowed)}")
+        if out.dim() != 2 or tuple(out.shape) != (M, N):
+            raise ValueError(f"out has shape {tuple(out.shape)}, expected ({M}, {N})")
+        if out.stride(1) != 1:
+            raise ValueError("out must have its N dimension contiguous")
+        self._on_device("out", out)
+        return out
+
+    _E4M3_TYPES = (torch.float8_e4m3fn, torch.uint8)
+
+    def _resolve_out(self, out, out_dtype, M: int, N: int, device):
+        """(output tensor, SL8_OUT_*) of the layers that can write bf16 or e4m3.  With `out` given its dtype
+        decides; an explicit out_dtype that contradicts it is an error."""
+        if out is None:
+            out_dtype = torch.bfloat16 if out_dtype is None else out_dtype
+            if out_dtype != torch.bfloat16 and out_dtype not in self._E4M3_TYPES:
+                raise TypeError("out_dtype must be bfloat16, float8_e4m3fn or uint8 (raw e4m3 codes)")
+            out = self._new_out(M, N, out_dtype, device)
+        else:
+            self._check_out(out, M, N, (torch.bfloat16,) + self._E4M3_TYPES)
+            if out_dtype is not None:
+                same = (out_dtype == out.dtype) or (out_dtype in self._E4M3_TYPES and out.dtype in self._E4M3_TYPES)
+                if not same:
+                    raise TypeError(f"out_dtype {out_dtype} contradicts out.dtype {out.dtype}")
+        return out, (_l.SL8_OUT_E4M3 if out.dtype in self._E4M3_TYPES else _l.SL8_OUT_BF16)
 
     # ------------------------------------------------------------------ layers
     def patch_embed(self, A, B, table, *, period: Optional[int] = None, scale_a=None, scale_b=None, row_phase: int = 0,
@@ -91,7 +133,9 @@ class Engine:
         if table.dtype != torch.bfloat16 or table.dim() != 2 or table.shape[1] != N or table.stride(1) != 1:
             raise ValueError("table must be bf16 [rows, N] with N contiguous")
         period = table.shape[0] if period is None else int(period)
-        D = self._new_out(M, N, torch.bfloat16, A.device) if out is None else out
+        for name, t in (("table", table), ("scale_a", scale_a), ("scale_b", scale_b)):
+            self._on_device(name, t)
+        D = self._new_out(M, N, torch.bfloat16, A.device) if out is None else self._check_out(out, M, N, (torch.bfloat16,))
         self._check(self._lib.sl8_patch_embed_fp8(
             self._h, A.data_ptr(), A.stride(0), B.data_ptr(), B.stride(0), _ptr(scale_a), _ptr(scale_b),
             table.data_ptr(), table.stride(0), period, table.shape[0], int(row_phase), D.data_ptr(), D.stride(0),
@@ -118,23 +162,25 @@ class Engine:
                                                       out.stride(0), rows, self._stream(stream)))
         return out
 
-    def fc1_gelu(self, A, B, bias, *, scale_a=None, scale_b=None, out_dtype=torch.bfloat16, out_scale=None,
+    def fc1_gelu(self, A, B, bias, *, scale_a=None, scale_b=None, out_dtype=None, out_scale=None,
                  out=None, flags: int = 0, stream=None) -> torch.Tensor:
-        """D = cast(gelu_tanh(sa*sb*A.B^T + bias) / out_scale); bias bf16 [N] (fp32 with SL8_FLAG_BIAS_F32)."""
+        """D = cast(gelu_tanh(sa*sb*A.B^T + bias) / out_scale); bias bf16 [N] (fp32 with SL8_FLAG_BIAS_F32).
+        The output type is that of ``out`` when it is given, else ``out_dtype`` (default bf16)."""
         M, N, K = self._operands(A, B)
         if bias is not None and bias.dtype == torch.float32:
             flags |= _l.SL8_FLAG_BIAS_F32
         elif bias is not None and bias.dtype != torch.bfloat16:
             raise TypeError("bias must be bf16 or fp32")
-        e4 = out_dtype in (torch.float8_e4m3fn, torch.uint8)
-        D = self._new_out(M, N, out_dtype, A.device) if out is None else out
+        for name, t in (("bias", bias), ("scale_a", scale_a), ("scale_b", scale_b), ("out_scale", out_scale)):
+            self._on_device(name, t)
+        D, out_code = self._resolve_out(out, out_dtype, M, N, A.device)
         self._check(self._lib.sl8_fc1_gelu_fp8(
             self._h, A.data_ptr(), A.stride(0), B.data_ptr(), B.stride(0), _ptr(scale_a), _ptr(scale_b), _ptr(bias),
-            D.data_ptr(), D.stride(0), _l.SL8_OUT_E4M3 if e4 else _l.SL8_OUT_BF16, _ptr(out_scale), M, N, K,
+            D.data_ptr(), D.stride(0), out_code, _ptr(out_scale), M, N, K,
             int(flags), self._stream(stream)))
         return D
 
-    def linear_bias(self, A, B, bias, *, scale_a=None, scale_b=None, out_dtype=torch.bfloat16, out_scale=None,
+    def linear_bias(self, A, B, bias, *, scale_a=None, scale_b=None, out_dtype=None, out_scale=None,
                     out=None, flags: int = 0, stream=None) -> torch.Tensor:
         """D = cast((sa*sb*A.B^T + bias) / out_scale): the Q / K / V projections (no activation)."""
         M, N, K = self._operands(A, B)
@@ -142,11 +188,12 @@ class Engine:
             flags |= _l.SL8_FLAG_BIAS_F32
         elif bias is not None and bias.dtype != torch.bfloat16:
             raise TypeError("bias must be bf16 or fp32")
-        e4 = out_dtype in (torch.float8_e4m3fn, torch.uint8)
-        D = self._new_out(M, N, out_dtype, A.device) if out is None else out
+        for name, t in (("bias", bias), ("scale_a", scale_a), ("scale_b", scale_b), ("out_scale", out_scale)):
+            self._on_device(name, t)
+        D, out_code = self._resolve_out(out, out_dtype, M, N, A.device)
         self._check(self._lib.sl8_linear_bias_fp8(
             self._h, A.data_ptr(), A.stride(0), B.data_ptr(), B.stride(0), _ptr(scale_a), _ptr(scale_b), _ptr(bias),
-            D.data_ptr(), D.stride(0), _l.SL8_OUT_E4M3 if e4 else _l.SL8_OUT_BF16, _ptr(out_scale), M, N, K,
+            D.data_ptr(), D.stride(0), out_code, _ptr(out_scale), M, N, K,
             int(flags), self._stream(stream)))
         return D
 
@@ -158,7 +205,9 @@ class Engine:
             flags |= _l.SL8_FLAG_BIAS_F32
         if residual.dtype != torch.bfloat16 or residual.shape != (M, N) or residual.stride(1) != 1:
             raise ValueError("residual must be bf16 [M, N] with N contiguous")
-        D = self._new_out(M, N, torch.bfloat16, A.device) if out is None else out
+        for name, t in (("bias", bias), ("residual", residual), ("scale_a", scale_a), ("scale_b", scale_b)):
+            self._on_device(name, t)
+        D = self._new_out(M, N, torch.bfloat16, A.device) if out is None else self._check_out(out, M, N, (torch.bfloat16,))
         self._check(self._lib.sl8_fc2_residual_fp8(
             self._h, A.data_ptr(), A.stride(0), B.data_ptr(), B.stride(0), _ptr(scale_a), _ptr(scale_b), _ptr(bias),
             residual.data_ptr(), residual.stride(0), D.data_ptr(), D.stride(0), M, N, K, int(flags),

@@ -70,3 +70,65 @@ def test_two_rank_sharding_gloo():
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     mp.spawn(_worker, args=(2, port, 129), nprocs=2, join=True)
+
+
+# ---- Engine argument validation: refused on the host, before any launch ---------------------------------------------
+class _FakeCuda:
+    """Stands in for a CUDA tensor where only its placement matters (no GPU is needed to test the refusal)."""
+
+    def __init__(self, index):
+        self.is_cuda = True
+        self.device = torch.device("cuda", index)
+
+
+def _bare_engine(device=0):
+    from siglip_b200.layers import Engine
+    eng = Engine.__new__(Engine)          # no handle: the checks under test run before the library is called
+    eng.device = device
+    eng._h = None
+    return eng
+
+
+def test_out_tensor_is_validated_before_launch():
+    eng = _bare_engine()
+    M, N = 8, 32
+    with pytest.raises(TypeError):        # a one-byte buffer where the layer writes bf16
+        eng._check_out(torch.empty((M, N), dtype=torch.uint8), M, N, (torch.bfloat16,))
+    with pytest.raises(ValueError):       # wrong shape
+        eng._check_out(torch.empty((M, N + 16), dtype=torch.bfloat16), M, N, (torch.bfloat16,))
+    with pytest.raises(ValueError):       # N not contiguous
+        eng._check_out(torch.empty((N, M), dtype=torch.bfloat16).t(), M, N, (torch.bfloat16,))
+    with pytest.raises(ValueError):       # host memory
+        eng._check_out(torch.empty((M, N), dtype=torch.bfloat16), M, N, (torch.bfloat16,))
+
+
+def test_output_type_comes_from_out():
+    from siglip_b200 import lib as l
+    eng = _bare_engine()
+    eng._on_device = lambda name, t: None                 # placement is covered by its own test
+    M, N = 8, 32
+    out8 = torch.empty((M, N), dtype=torch.uint8)
+    assert eng._resolve_out(out8, None, M, N, "cpu")[1] == l.SL8_OUT_E4M3            # no keyword needed
+    assert eng._resolve_out(out8, torch.float8_e4m3fn, M, N, "cpu")[1] == l.SL8_OUT_E4M3
+    out16 = torch.empty((M, N), dtype=torch.bfloat16)
+    assert eng._resolve_out(out16, None, M, N, "cpu")[1] == l.SL8_OUT_BF16
+    with pytest.raises(TypeError):        # the bf16 kernel must never be pointed at a one-byte buffer
+        eng._resolve_out(out8, torch.bfloat16, M, N, "cpu")
+    with pytest.raises(TypeError):
+        eng._resolve_out(out16, torch.uint8, M, N, "cpu")
+    with pytest.raises(TypeError):
+        eng._resolve_out(None, torch.float16, M, N, "cpu")
+    fresh, code = eng._resolve_out(None, None, M, N, "cpu")
+    assert fresh.dtype == torch.bfloat16 and code == l.SL8_OUT_BF16
+
+
+def test_operands_must_live_on_the_engines_gpu():
+    eng = _bare_engine(device=0)
+    eng._on_device("A", _FakeCuda(0))
+    eng._on_device("bias", None)
+    with pytest.raises(ValueError, match="cuda:1"):
+        eng._on_device("residual", _FakeCuda(1))
+    with pytest.raises(ValueError):
+        eng._on_device("table", torch.empty(4))
+    with pytest.raises(ValueError):       # fc1_gelu refuses host operands before touching the library
+        eng.fc1_gelu(torch.empty((4, 16), dtype=torch.uint8), torch.empty((16, 16), dtype=torch.uint8), None)

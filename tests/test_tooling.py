@@ -103,10 +103,3 @@ def test_result_line_of_the_reference_harness_is_parsed():
     line = "Custom kernel: 0.531 ms\n@@RESULT ms=0.531 tflops=2062.11 checksum=1769472.000000 valid=1 c0=1728.0\n"
     assert compare.parse_result_line(line) == pytest.approx(0.531)
     assert compare.parse_result_line("no result here") is None
-
-
-def test_tile_cost_fit():
-    """diagnose.fit_tile_cost: the line through two (k-blocks, time per tile) points."""
-    from siglip_b200.diagnose import fit_tile_cost
-    a, b = fit_tile_cost(9 * 375.0 + 1100.0, 9, 36 * 375.0 + 1100.0, 36)
-    assert abs(a - 375.0) < 1e-9 and abs(b - 1100.0) < 1e-9

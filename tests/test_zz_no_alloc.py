@@ -71,3 +71,7 @@ def test_static_entry_point_e4m3_and_errors(engine):
     bad = lib.sl8_fc1_gelu_fp8_static(p.A.data_ptr(), p.A.stride(0), p.B.data_ptr(), p.B.stride(0), None, None, None,
                                       got.data_ptr(), got.stride(0), L.SL8_OUT_E4M3, None, p.M, p.N, p.K, L.SL8_FLAG_PE_F32_ADD, None, None, None)
     assert bad == L.SL8_ERR_INVALID_VALUE
+    # a scale pointer that is not 4-byte aligned is refused on the host (the kernel would fault on it)
+    bad = lib.sl8_fc1_gelu_fp8_static(p.A.data_ptr(), p.A.stride(0), p.B.data_ptr(), p.B.stride(0), sa.data_ptr() + 2, None, None,
+                                      got.data_ptr(), got.stride(0), L.SL8_OUT_E4M3, None, p.M, p.N, p.K, 0, None, None, None)
+    assert bad == L.SL8_ERR_ALIGNMENT
