@@ -293,6 +293,9 @@ int sl8_set_wait_budget_ms(sl8_handle_t h, int ms);
  *   [12] epilogue warp 0 waiting until the previous store has read its staging buffer
  *   [13] epilogue warp 0 issuing the side-data prefetch
  *   [14] MMA thread issuing tcgen05.mma         [15] MMA thread issuing tcgen05.commit
+ * sl8_trace_enable(h, 2) records the totals and the once-per-tile waits only ([1], [3], [4], [5], [6], [8]; [2] then counts the k-blocks
+ * whose operands had not landed one k-block ahead): the roles then run the same code paths as
+ * without tracing, so [4] is the kernel's duration in SM clock cycles (divide by the event time for the SM clock).
  * sl8_trace_read synchronises the device and copies min(grid of the last launch, max_blocks)
  * records into out[max_blocks * SL8_TRACE_SLOTS]; returns the number of records or an error. */
 #define SL8_TRACE_SLOTS 16

@@ -244,13 +244,22 @@ int run(sl8_handle_t h, const Problem& q, cudaStream_t stream) {
         h->smem_attr_set[vid][slot] = true;
     }
 
-    CUtensorMap map_a, map_b, map_d;
+    CUtensorMap map_a, map_b, map_bt, map_d;
     rc = encode_2d(h, &map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q.A, (unsigned long long)q.K, (unsigned long long)q.M,
                    (unsigned long long)q.lda, 128, 128, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
     if (rc != SL8_OK) return rc;
     rc = encode_2d(h, &map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q.B, (unsigned long long)q.K, (unsigned long long)q.N,
                    (unsigned long long)q.ldb, 128, (unsigned)(v->tn / v->cg), CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
     if (rc != SL8_OK) return rc;
+    // The last N tile is as wide as what is left of N (a multiple of 16): its MMAs run with that N and each CTA
+    // brings tail / cta_group rows of B per k-block through a second map with a box of that height.
+    const int tail_cols = q.N % v->tn == 0 ? v->tn : q.N % v->tn;
+    map_bt = map_b;
+    if (tail_cols != v->tn) {
+        rc = encode_2d(h, &map_bt, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q.B, (unsigned long long)q.K, (unsigned long long)q.N,
+                       (unsigned long long)q.ldb, 128, (unsigned)(tail_cols / v->cg), CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+        if (rc != SL8_OK) return rc;
+    }
     // Staging rows (= store boxes) are 128 bytes wide, 64 where one epilogue warp's columns fill no more.
     const int row_bytes = (v->tn / (v->epi_warps / 4)) * ob < 128 ? 64 : 128;
     rc = encode_2d(h, &map_d, ob == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, ob, q.D,
@@ -285,6 +294,7 @@ int run(sl8_handle_t h, const Problem& q, cudaStream_t stream) {
     p.k_blocks = (q.K + v->tk - 1) / v->tk;
     const int k_last = q.K - (p.k_blocks - 1) * v->tk;
     p.last_kblock_mmas = (k_last + 31) / 32;
+    p.tail_cols = tail_cols;
     p.scale_a = q.scale_a;
     p.scale_b = q.scale_b;
     p.out_scale = q.out_scale;
@@ -296,7 +306,7 @@ int run(sl8_handle_t h, const Problem& q, cudaStream_t stream) {
     p.table_rows = q.table_rows;
     p.D = q.D;
     p.ldd = q.ldd;
-    p.flags = q.flags;
+    p.flags = q.flags | (h->trace_coarse ? sl8::FLAG_COARSE_TRACE : 0u);
     p.wait_budget_ms = h->wait_budget_ms;
     p.status = h->d_status;
     p.prof = h->d_prof;
@@ -304,7 +314,7 @@ int run(sl8_handle_t h, const Problem& q, cudaStream_t stream) {
     const int grid = grid_for(h, v, slot, p.num_tiles);
     h->last_grid = grid;
     if (h->d_prof && grid > h->prof_blocks) return fail(h, SL8_ERR_INVALID_VALUE, "tracing buffer smaller than the grid");
-    cudaError_t e = v->launch[slot](&map_a, &map_b, &map_d, &map_s, &p, grid, stream);
+    cudaError_t e = v->launch[slot](&map_a, &map_b, &map_bt, &map_d, &map_s, &p, grid, stream);
     if (e != cudaSuccess) return fail_cuda(h, e, "kernel launch");
     return SL8_OK;
 }
@@ -395,11 +405,14 @@ SL8_API int sl8_destroy(sl8_handle_t h) {
             if (pp.d_a[i]) cudaFree(pp.d_a[i]);
             if (pp.d_r[i]) cudaFree(pp.d_r[i]);
             if (pp.d_d[i]) cudaFree(pp.d_d[i]);
+            if (pp.d_h[i]) cudaFree(pp.d_h[i]);
             if (pp.stream[i]) cudaStreamDestroy(pp.stream[i]);
         }
         if (pp.consts_ready) cudaEventDestroy(pp.consts_ready);
         if (pp.d_b) cudaFree(pp.d_b);
         if (pp.d_bias) cudaFree(pp.d_bias);
+        if (pp.d_b2) cudaFree(pp.d_b2);
+        if (pp.d_bias2) cudaFree(pp.d_bias2);
         if (pp.d_table) cudaFree(pp.d_table);
         if (pp.d_scales) cudaFree(pp.d_scales);
         if (pp.h_scales) cudaFreeHost(pp.h_scales);
@@ -488,6 +501,21 @@ long long slab_rows_for(long long M, int N, int K, int out_bytes, bool has_res) 
     return rows;
 }
 
+// Streams, the constants-uploaded event and the scale staging of the host-operand pipeline, created on first use.
+int pipe_init(sl8_handle_t h) {
+    HostPipe& pp = h->pipe;
+    if (pp.ready) return SL8_OK;
+    cudaError_t e;
+    for (int i = 0; i < HostPipe::SLOTS; i++) {
+        if (!pp.stream[i] && (e = cudaStreamCreateWithFlags(&pp.stream[i], cudaStreamNonBlocking)) != cudaSuccess) return fail_cuda(h, e, "cudaStreamCreate");
+    }
+    if (!pp.consts_ready && (e = cudaEventCreateWithFlags(&pp.consts_ready, cudaEventDisableTiming)) != cudaSuccess) return fail_cuda(h, e, "cudaEventCreate");
+    if (!pp.d_scales && (e = cudaMalloc(reinterpret_cast<void**>(&pp.d_scales), 16)) != cudaSuccess) return fail_cuda(h, e, "cudaMalloc(scales)");
+    if (!pp.h_scales && (e = cudaMallocHost(reinterpret_cast<void**>(&pp.h_scales), 16)) != cudaSuccess) return fail_cuda(h, e, "cudaMallocHost(scales)");
+    pp.ready = true;
+    return SL8_OK;
+}
+
 int run_host(sl8_handle_t h, Problem q, float scale_a, float scale_b, float out_scale) {
     if (!h) return SL8_ERR_INVALID_VALUE;
     if (!q.A || !q.B || !q.D) return fail(h, SL8_ERR_INVALID_VALUE, "A, B and D must not be NULL");
@@ -508,21 +536,9 @@ int run_host(sl8_handle_t h, Problem q, float scale_a, float scale_b, float out_
     if (!guard.ok) return fail(h, SL8_ERR_CUDA, "cudaSetDevice failed");
     HostPipe& pp = h->pipe;
     cudaError_t e;
-    if (!pp.ready) {
-        for (int i = 0; i < HostPipe::SLOTS; i++) {
-            e = cudaStreamCreateWithFlags(&pp.stream[i], cudaStreamNonBlocking);
-            if (e != cudaSuccess) return fail_cuda(h, e, "cudaStreamCreate");
-        }
-        e = cudaEventCreateWithFlags(&pp.consts_ready, cudaEventDisableTiming);
-        if (e != cudaSuccess) return fail_cuda(h, e, "cudaEventCreate");
-        e = cudaMalloc(reinterpret_cast<void**>(&pp.d_scales), 16);
-        if (e != cudaSuccess) return fail_cuda(h, e, "cudaMalloc(scales)");
-        e = cudaMallocHost(reinterpret_cast<void**>(&pp.h_scales), 16);
-        if (e != cudaSuccess) return fail_cuda(h, e, "cudaMallocHost(scales)");
-        pp.ready = true;
-    }
+    int rc = pipe_init(h);
+    if (rc != SL8_OK) return rc;
     const long long slab = slab_rows_for(q.M, q.N, q.K, ob, has_res);
-    int rc;
     for (int i = 0; i < HostPipe::SLOTS; i++) {
         size_t ha = pp.a_bytes, hd = pp.d_bytes, hr = pp.r_bytes;
         if ((rc = ensure(h, &pp.d_a[i], &ha, (size_t)slab * q.lda)) != SL8_OK) return rc;
@@ -622,6 +638,129 @@ SL8_API int sl8_fc2_residual_fp8_host(sl8_handle_t h, const void* A, int64_t lda
     return run_host(h, q, scale_a, scale_b, 1.0f);
 }
 
+// =========================================================================== FC1 -> FC2 chain
+
+namespace {
+
+struct ChainArgs {
+    const void* A; long long lda;
+    const void* W1; long long ldw1; const void* bias1;
+    const void* W2; long long ldw2; const void* bias2;
+    const void* residual; long long ldr;
+    void* D; long long ldd;
+    long long M; int d_model, d_ff;
+    unsigned flags;
+};
+
+// The two launches of the MLP on device operands: hidden = e4m3(gelu(A.W1^T + b1) / hidden_scale), D = hidden.W2^T + b2 + R.
+int run_chain(sl8_handle_t h, const ChainArgs& c, const float* scale_a, const float* scale_w1, const float* scale_w2,
+              const float* hidden_scale, void* hidden, long long ld_hidden, cudaStream_t stream) {
+    if (!hidden || !hidden_scale) return fail(h, SL8_ERR_INVALID_VALUE, "hidden buffer and hidden_scale must not be NULL");
+    if (c.flags & ~(unsigned)(SL8_FLAG_BIAS_F32 | SL8_FLAG_GELU_HW_TANH)) return fail(h, SL8_ERR_INVALID_VALUE, "unknown flag bits");
+    Problem q1 = {};
+    q1.op = SL8_OP_FC1_GELU; q1.out_dtype = SL8_OUT_E4M3;
+    q1.A = c.A; q1.lda = c.lda; q1.B = c.W1; q1.ldb = c.ldw1;
+    q1.scale_a = scale_a; q1.scale_b = scale_w1; q1.out_scale = hidden_scale;
+    q1.bias = c.bias1;
+    q1.D = hidden; q1.ldd = ld_hidden; q1.M = c.M; q1.N = c.d_ff; q1.K = c.d_model; q1.flags = c.flags;
+    int rc = run(h, q1, stream);
+    if (rc != SL8_OK) return rc;
+    Problem q2 = {};
+    q2.op = SL8_OP_FC2_RESIDUAL; q2.out_dtype = SL8_OUT_BF16;
+    q2.A = hidden; q2.lda = ld_hidden; q2.B = c.W2; q2.ldb = c.ldw2;
+    q2.scale_a = hidden_scale; q2.scale_b = scale_w2;
+    q2.bias = c.bias2; q2.side = c.residual; q2.ld_side = c.ldr;
+    q2.D = c.D; q2.ldd = c.ldd; q2.M = c.M; q2.N = c.d_model; q2.K = c.d_ff; q2.flags = c.flags & SL8_FLAG_BIAS_F32;
+    return run(h, q2, stream);
+}
+
+}  // namespace
+
+SL8_API int sl8_mlp_chain_fp8(sl8_handle_t h, const void* A, int64_t lda, const void* W1, int64_t ldw1,
+                              const float* scale_a, const float* scale_w1, const void* bias1, void* hidden,
+                              int64_t ld_hidden, const float* hidden_scale, const void* W2, int64_t ldw2,
+                              const float* scale_w2, const void* bias2, const void* residual, int64_t ldr, void* D,
+                              int64_t ldd, int64_t M, int d_model, int d_ff, unsigned flags, sl8_stream_t stream) {
+    if (!h) return SL8_ERR_INVALID_VALUE;
+    ChainArgs c = {A, lda, W1, ldw1, bias1, W2, ldw2, bias2, residual, ldr, D, ldd, M, d_model, d_ff, flags};
+    return run_chain(h, c, scale_a, scale_w1, scale_w2, hidden_scale, hidden, ld_hidden, static_cast<cudaStream_t>(stream));
+}
+
+SL8_API int sl8_mlp_chain_fp8_host(sl8_handle_t h, const void* A, int64_t lda, const void* W1, int64_t ldw1, float scale_a,
+                                   float scale_w1, const void* bias1, float hidden_scale, const void* W2, int64_t ldw2,
+                                   float scale_w2, const void* bias2, const void* residual, int64_t ldr, void* D,
+                                   int64_t ldd, int64_t M, int d_model, int d_ff, unsigned flags) {
+    if (!h) return SL8_ERR_INVALID_VALUE;
+    if (!A || !W1 || !W2 || !residual || !D) return fail(h, SL8_ERR_INVALID_VALUE, "A, W1, W2, residual and D must not be NULL");
+    if (M < 1 || d_model < 1 || d_ff < 1) return fail(h, SL8_ERR_INVALID_VALUE, "M, d_model, d_ff must be positive");
+    if (lda < d_model || ldw1 < d_model || ldw2 < d_ff || ldr < d_model || ldd < d_model) return fail(h, SL8_ERR_INVALID_VALUE, "leading dimension too small");
+    if (lda % 16 || ldw1 % 16 || ldw2 % 16 || (ldr * 2) % 16 || (ldd * 2) % 16) return fail(h, SL8_ERR_ALIGNMENT, "row pitches must be multiples of 16 bytes");
+    if (!(hidden_scale > 0.0f)) return fail(h, SL8_ERR_INVALID_VALUE, "hidden_scale must be positive");
+
+    std::lock_guard<std::mutex> pipe_lock(h->pipe_mu);
+    DeviceGuard guard(h->device);
+    if (!guard.ok) return fail(h, SL8_ERR_CUDA, "cudaSetDevice failed");
+    HostPipe& pp = h->pipe;
+    int rc = pipe_init(h);
+    if (rc != SL8_OK) return rc;
+    // Rows per slab: about 64 MiB of traffic over the bus (A up, residual up, D down); the hidden slab stays on the GPU.
+    const long long ld_hidden = ((long long)d_ff + 127) / 128 * 128;
+    long long slab = (long long)(64.0 * 1024 * 1024 / ((double)d_model * 5.0));
+    slab = slab / 256 * 256;
+    if (slab < 256) slab = 256;
+    if (slab > M) slab = M;
+    for (int i = 0; i < HostPipe::SLOTS; i++) {
+        size_t ha = pp.a_bytes, hd = pp.d_bytes, hr = pp.r_bytes, hh = pp.h_bytes;
+        if ((rc = ensure(h, &pp.d_a[i], &ha, (size_t)slab * lda)) != SL8_OK) return rc;
+        if ((rc = ensure(h, &pp.d_d[i], &hd, (size_t)slab * ldd * 2)) != SL8_OK) return rc;
+        if ((rc = ensure(h, &pp.d_r[i], &hr, (size_t)slab * ldr * 2)) != SL8_OK) return rc;
+        if ((rc = ensure(h, &pp.d_h[i], &hh, (size_t)slab * ld_hidden)) != SL8_OK) return rc;
+        if (i == HostPipe::SLOTS - 1) { pp.a_bytes = ha; pp.d_bytes = hd; pp.r_bytes = hr; pp.h_bytes = hh; }
+    }
+    const size_t b1 = (size_t)d_ff * ((flags & SL8_FLAG_BIAS_F32) ? 4 : 2), b2 = (size_t)d_model * ((flags & SL8_FLAG_BIAS_F32) ? 4 : 2);
+    if ((rc = ensure(h, &pp.d_b, &pp.b_bytes, (size_t)d_ff * ldw1)) != SL8_OK) return rc;
+    if ((rc = ensure(h, &pp.d_b2, &pp.b2_bytes, (size_t)d_model * ldw2)) != SL8_OK) return rc;
+    if (bias1 && (rc = ensure(h, &pp.d_bias, &pp.bias_bytes, b1)) != SL8_OK) return rc;
+    if (bias2 && (rc = ensure(h, &pp.d_bias2, &pp.bias2_bytes, b2)) != SL8_OK) return rc;
+
+    cudaError_t e;
+    auto bail = [&](cudaError_t err, const char* what) {
+        cudaDeviceSynchronize();
+        (void)cudaGetLastError();
+        return fail_cuda(h, err, what);
+    };
+    cudaStream_t s0 = pp.stream[0];
+    pp.h_scales[0] = scale_a; pp.h_scales[1] = scale_w1; pp.h_scales[2] = hidden_scale; pp.h_scales[3] = scale_w2;
+    if ((e = cudaMemcpyAsync(pp.d_scales, pp.h_scales, 16, cudaMemcpyHostToDevice, s0)) != cudaSuccess) return bail(e, "upload of the scales");
+    if ((e = cudaMemcpyAsync(pp.d_b, W1, (size_t)d_ff * ldw1, cudaMemcpyHostToDevice, s0)) != cudaSuccess) return bail(e, "upload of W1");
+    if ((e = cudaMemcpyAsync(pp.d_b2, W2, (size_t)d_model * ldw2, cudaMemcpyHostToDevice, s0)) != cudaSuccess) return bail(e, "upload of W2");
+    if (bias1 && (e = cudaMemcpyAsync(pp.d_bias, bias1, b1, cudaMemcpyHostToDevice, s0)) != cudaSuccess) return bail(e, "upload of bias1");
+    if (bias2 && (e = cudaMemcpyAsync(pp.d_bias2, bias2, b2, cudaMemcpyHostToDevice, s0)) != cudaSuccess) return bail(e, "upload of bias2");
+    if ((e = cudaEventRecord(pp.consts_ready, s0)) != cudaSuccess) return bail(e, "upload of constants");
+
+    const uint8_t* hA = static_cast<const uint8_t*>(A);
+    const uint8_t* hR = static_cast<const uint8_t*>(residual);
+    uint8_t* hD = static_cast<uint8_t*>(D);
+    int slot = 0;
+    for (long long r0 = 0; r0 < M; r0 += slab, slot = (slot + 1) % HostPipe::SLOTS) {
+        const long long rows = (r0 + slab < M) ? slab : M - r0;
+        cudaStream_t s = pp.stream[slot];
+        if ((slot != 0 || r0 == 0) && (e = cudaStreamWaitEvent(s, pp.consts_ready, 0)) != cudaSuccess) return bail(e, "wait for the constants");
+        if ((e = cudaMemcpyAsync(pp.d_a[slot], hA + (size_t)r0 * lda, (size_t)rows * lda, cudaMemcpyHostToDevice, s)) != cudaSuccess) return bail(e, "upload of a slab of A");
+        if ((e = cudaMemcpyAsync(pp.d_r[slot], hR + (size_t)r0 * ldr * 2, (size_t)rows * ldr * 2, cudaMemcpyHostToDevice, s)) != cudaSuccess) return bail(e, "upload of a slab of the residual");
+        ChainArgs c = {pp.d_a[slot], lda, pp.d_b, ldw1, bias1 ? pp.d_bias : nullptr, pp.d_b2, ldw2, bias2 ? pp.d_bias2 : nullptr,
+                       pp.d_r[slot], ldr, pp.d_d[slot], ldd, rows, d_model, d_ff, flags};
+        rc = run_chain(h, c, pp.d_scales, pp.d_scales + 1, pp.d_scales + 3, pp.d_scales + 2, pp.d_h[slot], ld_hidden, s);
+        if (rc != SL8_OK) { cudaDeviceSynchronize(); return rc; }
+        if ((e = cudaMemcpyAsync(hD + (size_t)r0 * ldd * 2, pp.d_d[slot], (size_t)rows * ldd * 2, cudaMemcpyDeviceToHost, s)) != cudaSuccess) return bail(e, "download of a slab of D");
+    }
+    for (int i = 0; i < HostPipe::SLOTS; i++) {
+        e = cudaStreamSynchronize(pp.stream[i]);
+        if (e != cudaSuccess) return fail_cuda(h, e, "host-operand pipeline");
+    }
+    return SL8_OK;
+}
+
 // =========================================================================== dispatch
 
 SL8_API int sl8_num_variants(void) { return SL8_NUM_VARIANTS; }
@@ -692,6 +831,7 @@ SL8_API int sl8_trace_enable(sl8_handle_t h, int on) {
     if (!h) return SL8_ERR_INVALID_VALUE;
     std::lock_guard<std::mutex> lock(h->mu);
     DeviceGuard guard(h->device);
+    h->trace_coarse = (on == 2);
     if (on && !h->d_prof) {
         const int blocks = 2 * h->sm_count;
         cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&h->d_prof), sizeof(long long) * sl8::PROF_SLOTS * blocks);

@@ -26,11 +26,14 @@ struct Sl8HostPipe {
     void* d_a[SLOTS] = {nullptr, nullptr, nullptr};
     void* d_r[SLOTS] = {nullptr, nullptr, nullptr};
     void* d_d[SLOTS] = {nullptr, nullptr, nullptr};
-    size_t a_bytes = 0, r_bytes = 0, d_bytes = 0;
+    void* d_h[SLOTS] = {nullptr, nullptr, nullptr};   // hidden activations of the FC1 -> FC2 chain (never leave the GPU)
+    size_t a_bytes = 0, r_bytes = 0, d_bytes = 0, h_bytes = 0;
     void* d_b = nullptr;      size_t b_bytes = 0;
     void* d_bias = nullptr;   size_t bias_bytes = 0;
+    void* d_b2 = nullptr;     size_t b2_bytes = 0;     // second weight matrix and bias of the chain
+    void* d_bias2 = nullptr;  size_t bias2_bytes = 0;
     void* d_table = nullptr;  size_t table_bytes = 0;
-    float* d_scales = nullptr;   // scale_a, scale_b, out_scale
+    float* d_scales = nullptr;   // scale_a, scale_b, out_scale (chain: scale_a, scale_w1, hidden_scale, scale_w2)
     float* h_scales = nullptr;   // pinned twin
     bool ready = false;
 };
@@ -54,6 +57,7 @@ struct sl8_context {
     uint32_t* d_status = nullptr;       // 4 words
     long long* d_prof = nullptr;        // tracing buffer, PROF_SLOTS per CTA, or null
     int prof_blocks = 0;
+    bool trace_coarse = false;          // sl8_trace_enable(h, 2): per-role totals only, untimed code paths
     int last_grid = 0;
     sl8_encode_tiled_fn encode = nullptr;
     int forced_variant = -1;

@@ -5,9 +5,14 @@
 // counterpart of the reference's persistent_gemm<EpilogueOp> (kernel_body.cuh:448-815) and
 // epilogue_store (kernel_body.cuh:47-442), rebuilt around run-time M/N/K:
 //
-//   warp 0        TMA producer: streams A[128 x 128B] and B[TN/CG x 128B] k-blocks into a
-//                 ring of STAGES shared-memory stages (SWIZZLE_128B), one mbarrier pair
-//                 (full / empty) per stage.
+//   warp 0        TMA producer of A: streams A[128 x 128B] k-blocks into a ring of STAGES
+//                 shared-memory stages (SWIZZLE_128B), one mbarrier pair (full / empty) per stage,
+//                 and announces the stage's bytes.
+//   warp 3 + EPI  TMA producer of B: streams B[TN/CG x 128B] k-blocks into the same stages.  Two
+//                 issuing threads because a thread's next bulk-tensor copy is not accepted before the
+//                 TMA unit has generated the requests of its previous one (2 cycles per 128-byte row:
+//                 64 bytes per clock per issuing thread, measured), while the unit itself serves two
+//                 threads at once at 128 bytes per clock: one thread cannot feed a 256 x 256 tile.
 //   warp 1        allocates tensor memory; one thread of the leader CTA issues
 //                 tcgen05.mma kind::f8f6f4 (E4M3 x E4M3 -> FP32 in TMEM), four K=32 steps per
 //                 k-block (fewer in the K tail), and commits to the stage's empty barrier and,
@@ -53,7 +58,10 @@ enum : int { OUT_BF16 = 0, OUT_E4M3 = 1 };
 #define SL8_DBG(flags, bit) false
 #endif
 
+// FLAG_COARSE_TRACE (set by the library, never by a caller): with tracing on, record only the per-role totals; the
+// roles then run their untimed code paths, so the totals are those of the kernel as it runs without tracing.
 enum : unsigned { FLAG_BIAS_F32 = 1u, FLAG_PE_F32_ADD = 2u, FLAG_NO_ACTIVATION = 4u, FLAG_GELU_HW_TANH = 8u,
+                  FLAG_COARSE_TRACE = 0x40000000u,
                   DBG_SKIP_SIDE = 0x100u, DBG_SKIP_GELU = 0x200u, DBG_SKIP_BIAS = 0x400u, DBG_SKIP_STORE = 0x800u,
                   DBG_SKIP_LOAD = 0x1000u, DBG_SKIP_EPILOGUE = 0x2000u, DBG_SKIP_MMA = 0x4000u,
                   DBG_SKIP_A = 0x8000u, DBG_SKIP_B = 0x10000u, DBG_SKIP_TMEM_LD = 0x20000u, DBG_SKIP_MATH = 0x40000u,
@@ -99,6 +107,7 @@ struct KernelParams {
     int num_tiles;
     int k_blocks;          // ceil(K / TILE_K)
     int last_kblock_mmas;  // K = 32 steps needed in the last k-block (1 .. TILE_K / 32)
+    int tail_cols;         // columns of the last N tile: N - (tiles_n - 1) * TN, a multiple of 16 (== TN when N % TN == 0)
     const float* scale_a;
     const float* scale_b;
     const float* out_scale;
@@ -150,7 +159,7 @@ struct KernelTraits {
     // bias of column l of each 32-column chunk) and broadcasts by warp shuffle.
     static constexpr bool BIAS_IN_SMEM = 1024 + STAGES * STAGE_BYTES + STAGING_BYTES + EPI_WARPS * COLS_PER_WARP * 4 + 512 <= 232448;
     static constexpr int BIAS_BYTES = BIAS_IN_SMEM ? EPI_WARPS * COLS_PER_WARP * 4 : 0;
-    static constexpr int THREADS = (3 + EPI_WARPS) * 32;         // producer, MMA, epilogue warps, side-data loader
+    static constexpr int THREADS = (4 + EPI_WARPS) * 32;         // A producer, MMA, epilogue warps, side-data loader, B producer
     static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STAGING_BYTES + BIAS_BYTES + BAR_BYTES;
     static_assert(STAGE_BYTES % 1024 == 0, "every operand tile must start on a swizzle-atom boundary");
     static_assert(COLS_PER_WARP % REGION_COLS == 0, "a warp stores whole staging regions");
@@ -364,10 +373,10 @@ __device__ __forceinline__ void load_bias(float (&b)[NB], const void* bias, unsi
 }
 
 template <int CG, int TN, int TK, int STAGES, int EPI_WARPS, int OP, int OUT, int NBUF>
-__global__ void __launch_bounds__((3 + EPI_WARPS) * 32, 1)
+__global__ void __launch_bounds__((4 + EPI_WARPS) * 32, 1)
 sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_s,
-                const KernelParams p) {
+                const __grid_constant__ CUtensorMap map_bt, const __grid_constant__ CUtensorMap map_d,
+                const __grid_constant__ CUtensorMap map_s, const KernelParams p) {
     using T = KernelTraits<CG, TN, TK, STAGES, EPI_WARPS, OUT, NBUF>;
 
     extern __shared__ uint8_t smem_raw[];
@@ -410,6 +419,7 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         *abort_flag = 0u;
         prefetch_tensormap(&map_a);
         prefetch_tensormap(&map_b);
+        prefetch_tensormap(&map_bt);
         prefetch_tensormap(&map_d);
         if constexpr (OP != OP_FC1) prefetch_tensormap(&map_s);
     }
@@ -444,13 +454,21 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const uint32_t tmem_base = *tmem_ptr;
 
     // ---------------------------------------------------------------- roles
-    if (warp == 0) {
-        // ===== TMA producer =====
+    if (warp == 0 || warp == 3 + EPI_WARPS) {
+        // ===== TMA producers: warp 0 brings A, the last warp brings B =====
+        // Both wait for the stage to be free and then issue their own copies.  Only the A producer arrives on
+        // the stage's full barrier (in a CTA pair: only the leader's), announcing the bytes of everything that
+        // will land on it; the other copies just count down.  The transaction count may run negative until
+        // that arrive lands, and the phase cannot complete before it.  A B copy can never be a whole phase
+        // ahead of the arrive it belongs to: the stage is only handed back (empty barrier) after the MMAs have
+        // read it, i.e. after the previous phase of the full barrier completed, arrive included.
         if (lane == 0) {
+            const bool is_a = (warp == 0);
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            const bool prof = p.prof != nullptr;
+            const bool prof_total = p.prof != nullptr && is_a;
+            const bool prof = prof_total && !(p.flags & (FLAG_COARSE_TRACE | DBG_COARSE_TRACE));
             const uint32_t full_bar_leader = (CG == 2) ? map_to_cta(full_bar0, 0) : full_bar0;
             long long t_wait = 0;
             const long long t_begin = clock64();
@@ -459,7 +477,13 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const int tm = tile / p.tiles_n;
                 const int tn = tile - tm * p.tiles_n;
                 const int m0 = tm * (T::TILE_M_CTA * CG) + static_cast<int>(cta_rank) * T::TILE_M_CTA;
-                const int nb = tn * TN + static_cast<int>(cta_rank) * T::B_ROWS;
+                // The last N tile may be narrower: each CTA of a pair then holds tail_cols / CG rows of B,
+                // brought by a tensor map whose box is that tall (map_bt), and the MMAs are issued with N = tail_cols.
+                const bool tail = (tn == p.tiles_n - 1) && (p.tail_cols != TN);
+                const int b_rows = tail ? p.tail_cols / CG : T::B_ROWS;
+                const int nb = tn * TN + static_cast<int>(cta_rank) * b_rows;
+                const uint32_t stage_tx = static_cast<uint32_t>(T::A_BYTES + T::KATOMS * b_rows * 128);
+                const CUtensorMap* const bmap = tail ? &map_bt : &map_b;
                 for (int kb = 0; kb < p.k_blocks; kb++) {
                     const long long t0 = prof ? clock64() : 0;
                     ok = wait_bar<SL8_SPIN_CRITICAL>(empty_bar0 + 8 * stage, phase ^ 1u, wc, ST_PRODUCER_EMPTY_WAIT, stage);
@@ -468,32 +492,36 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     const uint32_t a_dst = base + stage * T::STAGE_BYTES;
                     const uint32_t b_dst = a_dst + T::A_BYTES;
                     if (SL8_DBG(p.flags, DBG_SKIP_LOAD)) {   // measurement aid: MMAs run on whatever shared memory holds
-                        if (cta_rank == 0) mbar_arrive(full_bar0 + 8 * stage);
+                        if (cta_rank == 0 && is_a) mbar_arrive(full_bar0 + 8 * stage);
                     } else if constexpr (CG == 2) {
-                        // Both CTAs' copies complete on the LEADER's barrier.  Only the leader arrives on it,
-                        // announcing the bytes of the whole pair; the peer's copies just count down (the
-                        // transaction count may run negative until the leader's arrive lands, and the phase
-                        // cannot complete before that arrive).
                         const uint32_t bar = full_bar_leader + 8 * stage;
-                        if (cta_rank == 0) mbar_arrive_expect_tx(full_bar0 + 8 * stage, 2 * T::STAGE_BYTES);
+                        if (is_a) {
+                            if (cta_rank == 0) mbar_arrive_expect_tx(full_bar0 + 8 * stage, 2 * stage_tx);
 #pragma unroll
-                        for (int a = 0; a < T::KATOMS; a++) {
-                            tma_load_2d_pair(a_dst + a * T::A_ATOM_BYTES, &map_a, kb * T::TILE_K + 128 * a, m0, bar);
-                            tma_load_2d_pair(b_dst + a * T::B_ATOM_BYTES, &map_b, kb * T::TILE_K + 128 * a, nb, bar);
+                            for (int a = 0; a < T::KATOMS; a++)
+                                tma_load_2d_pair(a_dst + a * T::A_ATOM_BYTES, &map_a, kb * T::TILE_K + 128 * a, m0, bar);
+                        } else {
+#pragma unroll
+                            for (int a = 0; a < T::KATOMS; a++)
+                                tma_load_2d_pair(b_dst + a * T::B_ATOM_BYTES, bmap, kb * T::TILE_K + 128 * a, nb, bar);
                         }
                     } else {
                         const uint32_t bar = full_bar0 + 8 * stage;
-                        mbar_arrive_expect_tx(bar, T::STAGE_BYTES);
+                        if (is_a) {
+                            mbar_arrive_expect_tx(bar, stage_tx);
 #pragma unroll
-                        for (int a = 0; a < T::KATOMS; a++) {
-                            tma_load_2d(a_dst + a * T::A_ATOM_BYTES, &map_a, kb * T::TILE_K + 128 * a, m0, bar);
-                            tma_load_2d(b_dst + a * T::B_ATOM_BYTES, &map_b, kb * T::TILE_K + 128 * a, nb, bar);
+                            for (int a = 0; a < T::KATOMS; a++)
+                                tma_load_2d(a_dst + a * T::A_ATOM_BYTES, &map_a, kb * T::TILE_K + 128 * a, m0, bar);
+                        } else {
+#pragma unroll
+                            for (int a = 0; a < T::KATOMS; a++)
+                                tma_load_2d(b_dst + a * T::B_ATOM_BYTES, bmap, kb * T::TILE_K + 128 * a, nb, bar);
                         }
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
-            if (prof) {
+            if (prof_total) {
                 long long* slot = p.prof + static_cast<size_t>(blockIdx.x) * PROF_SLOTS;
                 slot[PROF_PRODUCER_WAIT] = t_wait;
                 slot[PROF_PRODUCER_TOTAL] = clock64() - t_begin;
@@ -508,7 +536,9 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // the poll of the NEXT stage's barrier is issued before this stage's MMAs and read after them (the
         // blocking wait runs only if that look-ahead failed), and k-blocks are taken several per loop iteration.
         if (lane == 0 && cta_rank == 0) {
-            const uint32_t idesc = make_idesc_e4m3_f32(T::TILE_M_CTA * CG, TN);
+            const uint32_t idesc_full = make_idesc_e4m3_f32(T::TILE_M_CTA * CG, TN);
+            const uint32_t idesc_tail = make_idesc_e4m3_f32(T::TILE_M_CTA * CG, p.tail_cols);   // the last, narrower N tile
+            uint32_t idesc = idesc_full;
             // Descriptors differ between stages, atoms and K steps only in the 14-bit start-address
             // field: +2 there = 32 bytes = one K = 32 step inside the 128-byte row.
             const uint64_t adesc0 = make_kmajor_sw128_desc(base);
@@ -520,11 +550,7 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             uint32_t acc_phase = 0;
             bool ok = true;
             const bool prof_any = p.prof != nullptr;
-#ifdef SL8_DIAG
-            const bool prof = prof_any && !(p.flags & DBG_COARSE_TRACE);
-#else
-            const bool prof = prof_any;
-#endif
+            const bool prof = prof_any && !(p.flags & (FLAG_COARSE_TRACE | DBG_COARSE_TRACE));
             long long t_full = 0, t_tmem = 0, n_tiles = 0, t_mma = 0, t_commit = 0;
             const long long t_begin = clock64();
             uint32_t ready = 0;      // look-ahead: the barrier of `stage` was already seen complete
@@ -547,20 +573,24 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
             for (int tile = cluster_id; ok && tile < p.num_tiles; tile += num_clusters) {
                 wc.tile = tile;
-                long long t0 = prof ? clock64() : 0;
+                long long t0 = prof_any ? clock64() : 0;     // once per tile: timed in the coarse mode too
                 ok = wait_bar<SL8_SPIN_CRITICAL>(tempty_bar0 + 8 * acc, acc_phase ^ 1u, wc, ST_MMA_TMEM_EMPTY_WAIT, acc);
-                if (prof) t_tmem += clock64() - t0;
+                if (prof_any) t_tmem += clock64() - t0;
                 n_tiles++;
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * T::ACC_STRIDE;
+                idesc = (tile % p.tiles_n == p.tiles_n - 1) ? idesc_tail : idesc_full;
                 int kb = 0;
                 const int k_full = p.k_blocks - 1;           // k-blocks that hold all their MMAs
                 if (!prof && !SL8_DBG(p.flags, DBG_SKIP_MMA)) {
                     // One k-block: wait (only if the look-ahead failed), look ahead, MMAs, release the stage.
                     // n < 4 * KATOMS only in the K tail.
                     auto step = [&](bool fresh, int n) -> bool {
-                        if (!ready && !wait_bar<SL8_SPIN_CRITICAL>(full_bar0 + 8 * stage, phase, wc, ST_MMA_FULL_WAIT, stage)) return false;
+                        if (!ready) {      // the look-ahead saw the stage still filling: counted, then waited for
+                            t_full++;
+                            if (!wait_bar<SL8_SPIN_CRITICAL>(full_bar0 + 8 * stage, phase, wc, ST_MMA_FULL_WAIT, stage)) return false;
+                        }
                         const int s1 = (stage + 1 == STAGES) ? 0 : stage + 1;
                         const uint32_t ph1 = (s1 == 0) ? (phase ^ 1u) : phase;
                         const uint32_t r1 = mbar_test_wait(full_bar0 + 8 * s1, ph1);
@@ -691,7 +721,7 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         int acc = 0;
         uint32_t acc_phase = 0;
         const bool prof_total = p.prof != nullptr && ew == 0;
-        const bool prof = prof_total && !SL8_DBG(p.flags, DBG_COARSE_TRACE);   // inner timers cost ~35 cycles each
+        const bool prof = prof_total && !(p.flags & (FLAG_COARSE_TRACE | DBG_COARSE_TRACE));   // inner timers cost ~35 cycles each
         long long t_acc = 0, t_store = 0, t_ld = 0, t_math = 0, t_issue = 0, t_refill = 0;
         const long long t_begin = clock64();
         for (int tile = cluster_id; ok && tile < p.num_tiles; tile += num_clusters) {
@@ -709,12 +739,12 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             }
 
             // One lane polls; the others then confirm with a single try_wait of their own.
-            long long t0 = prof ? clock64() : 0;
+            long long t0 = prof_total ? clock64() : 0;       // once per tile: timed in the coarse mode too
             if (lane == 0) ok = wait_bar(tfull_bar0 + 8 * acc, acc_phase, wc, ST_EPI_TMEM_FULL_WAIT, acc);
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (ok && lane != 0) ok = wait_bar(tfull_bar0 + 8 * acc, acc_phase, wc, ST_EPI_TMEM_FULL_WAIT, acc);
             ok = __all_sync(0xffffffffu, ok);
-            if (prof) t_acc += clock64() - t0;
+            if (prof_total) t_acc += clock64() - t0;
             if (!ok) break;
             tc_fence_after();
 

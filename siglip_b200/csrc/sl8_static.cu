@@ -162,11 +162,16 @@ SL8_API int sl8_fc1_gelu_fp8_static(const void* A, int64_t lda, const void* B, i
     // The static scratch has room for SL8_STATIC_MAX_CTAS trace records: a larger grid does not fit.
     if (grid > kMaxCtas) return SL8_ERR_UNSUPPORTED;
 
-    CUtensorMap map_a, map_b, map_d;
+    CUtensorMap map_a, map_b, map_bt, map_d;
     if ((rc = encode_2d(s->encode, &map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, A, (unsigned long long)K, (unsigned long long)M,
                         (unsigned long long)lda, 128, 128, CU_TENSOR_MAP_L2_PROMOTION_L2_128B)) != SL8_OK) return rc;
     if ((rc = encode_2d(s->encode, &map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, B, (unsigned long long)K, (unsigned long long)N,
                         (unsigned long long)ldb, 128, (unsigned)(v->tn / v->cg), CU_TENSOR_MAP_L2_PROMOTION_L2_256B)) != SL8_OK) return rc;
+    const int tail_cols = N % v->tn == 0 ? v->tn : N % v->tn;    // the last N tile is as wide as what is left of N
+    map_bt = map_b;
+    if (tail_cols != v->tn &&
+        (rc = encode_2d(s->encode, &map_bt, CU_TENSOR_MAP_DATA_TYPE_UINT8, B, (unsigned long long)K, (unsigned long long)N,
+                        (unsigned long long)ldb, 128, (unsigned)(tail_cols / v->cg), CU_TENSOR_MAP_L2_PROMOTION_L2_256B)) != SL8_OK) return rc;
     if ((rc = encode_2d(s->encode, &map_d, ob == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, D,
                         (unsigned long long)N, (unsigned long long)M, (unsigned long long)ldd * ob, (unsigned)(128 / ob), 32,
                         CU_TENSOR_MAP_L2_PROMOTION_NONE)) != SL8_OK) return rc;
@@ -180,6 +185,7 @@ SL8_API int sl8_fc1_gelu_fp8_static(const void* A, int64_t lda, const void* B, i
     p.num_tiles = static_cast<int>(nt);
     p.k_blocks = (K + v->tk - 1) / v->tk;
     p.last_kblock_mmas = (K - (p.k_blocks - 1) * v->tk + 31) / 32;
+    p.tail_cols = tail_cols;
     p.scale_a = scale_a;
     p.scale_b = scale_b;
     p.out_scale = out_scale;
@@ -194,7 +200,7 @@ SL8_API int sl8_fc1_gelu_fp8_static(const void* A, int64_t lda, const void* B, i
 
     // The array still holds the previous call's status: it has to start at zero.
     if (cudaMemsetAsync(s->scratch, 0, 16, stream) != cudaSuccess) { (void)cudaGetLastError(); return SL8_ERR_CUDA; }
-    if (v->launch[slot](&map_a, &map_b, &map_d, &map_d, &p, grid, stream) != cudaSuccess) {
+    if (v->launch[slot](&map_a, &map_b, &map_bt, &map_d, &map_d, &p, grid, stream) != cudaSuccess) {
         (void)cudaGetLastError();
         return SL8_ERR_CUDA;
     }

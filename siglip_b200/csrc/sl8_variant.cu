@@ -13,7 +13,7 @@ namespace sl8 {
 namespace {
 
 template <int CG, int TN, int TK, int STAGES, int EW, int OP, int OUT, int NBUF>
-cudaError_t launch_one(const CUtensorMap* map_a, const CUtensorMap* map_b, const CUtensorMap* map_d,
+cudaError_t launch_one(const CUtensorMap* map_a, const CUtensorMap* map_b, const CUtensorMap* map_bt, const CUtensorMap* map_d,
                        const CUtensorMap* map_s, const KernelParams* params, int grid, cudaStream_t stream) {
     using T = KernelTraits<CG, TN, TK, STAGES, EW, OUT, NBUF>;
     cudaLaunchConfig_t cfg = {};
@@ -28,7 +28,7 @@ cudaError_t launch_one(const CUtensorMap* map_a, const CUtensorMap* map_b, const
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, sl8_gemm_kernel<CG, TN, TK, STAGES, EW, OP, OUT, NBUF>, *map_a, *map_b, *map_d, *map_s, *params);
+    return cudaLaunchKernelEx(&cfg, sl8_gemm_kernel<CG, TN, TK, STAGES, EW, OP, OUT, NBUF>, *map_a, *map_b, *map_bt, *map_d, *map_s, *params);
 }
 
 // Kernel pointer / launcher of one layer, or nulls where the variant cannot serve it.

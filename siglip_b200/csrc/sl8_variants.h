@@ -46,8 +46,10 @@ namespace sl8 {
 // Kernel slots of a variant: layer x output type.
 enum : int { K_PE = 0, K_FC1_BF16 = 1, K_FC1_E4M3 = 2, K_FC2 = 3, K_COUNT = 4 };
 
-typedef cudaError_t (*launch_fn)(const CUtensorMap* map_a, const CUtensorMap* map_b, const CUtensorMap* map_d,
-                                 const CUtensorMap* map_s, const KernelParams* params, int grid, cudaStream_t stream);
+// map_bt: B with a box as tall as one CTA's share of the last, narrower N tile (== map_b when N % tile N == 0).
+typedef cudaError_t (*launch_fn)(const CUtensorMap* map_a, const CUtensorMap* map_b, const CUtensorMap* map_bt,
+                                 const CUtensorMap* map_d, const CUtensorMap* map_s, const KernelParams* params, int grid,
+                                 cudaStream_t stream);
 
 struct VariantEntry {
     int id;

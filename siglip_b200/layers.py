@@ -323,8 +323,9 @@ class Engine:
                     "epi_wait_accumulator", "epi_total", "epi_wait_store", "tiles", "epi_wait_tmem_load",
                     "epi_math", "epi_store_issue", "epi_refill", "epi_prefetch_issue", "mma_issue", "mma_commit")
 
-    def trace_enable(self, on: bool = True) -> None:
-        self._check(self._lib.sl8_trace_enable(self._h, 1 if on else 0))
+    def trace_enable(self, on=True, coarse: bool = False) -> None:
+        """Tracing on / off; ``coarse`` records the per-role totals only and leaves the hot loops untimed."""
+        self._check(self._lib.sl8_trace_enable(self._h, (2 if coarse else 1) if on else 0))
 
     def trace_read(self, max_blocks: int = 512) -> list:
         """Per-CTA cycle totals of the last launch (see sl8_trace_read)."""
