@@ -249,6 +249,38 @@ int sl8_fc2_residual_fp8_host(sl8_handle_t h,
                               const void* residual, int64_t ldr,
                               void* D, int64_t ldd, int64_t M, int N, int K, unsigned flags);
 
+/* ---- the MLP of the block as one call: FC1 + GELU -> e4m3 -> FC2 + residual ---------------------------------
+ * The reference runs the two layers as two programs (fc1_gelu.cu, fc2.cu) and lists their hand-over as open work
+ * (docs/architecture.md:92-101); here FC1 writes e4m3 codes with a static scale straight into FC2's operand.
+ *   hidden = e4m3_sat_rne( gelu_tanh(sa*sw1 * A.W1^T + bias1) / *hidden_scale )      [M, d_ff], row pitch ld_hidden
+ *   D      = bf16( (*hidden_scale)*sw2 * hidden.W2^T + bias2 + residual )             [M, d_model]
+ * A [M, d_model] e4m3, W1 [d_ff, d_model] e4m3, W2 [d_model, d_ff] e4m3, biases bf16 (fp32 with SL8_FLAG_BIAS_F32),
+ * residual and D bf16 [M, d_model].  `hidden` is caller-owned scratch of M x ld_hidden bytes (ld_hidden >= d_ff, a
+ * multiple of 16; 128 recommended); hidden_scale must not be NULL.  Both launches go to `stream`; flags:
+ * SL8_FLAG_BIAS_F32, SL8_FLAG_GELU_HW_TANH.  Equivalent to sl8_fc1_gelu_fp8(..., SL8_OUT_E4M3, hidden_scale) followed
+ * by sl8_fc2_residual_fp8(hidden, ..., scale_a = hidden_scale). */
+int sl8_mlp_chain_fp8(sl8_handle_t h,
+                      const void* A, int64_t lda,
+                      const void* W1, int64_t ldw1, const float* scale_a, const float* scale_w1, const void* bias1,
+                      void* hidden, int64_t ld_hidden, const float* hidden_scale,
+                      const void* W2, int64_t ldw2, const float* scale_w2, const void* bias2,
+                      const void* residual, int64_t ldr,
+                      void* D, int64_t ldd,
+                      int64_t M, int d_model, int d_ff,
+                      unsigned flags, sl8_stream_t stream);
+
+/* The same with HOST operands: A and the residual go up, D comes down, slab by slab on three streams; the hidden
+ * activations never leave the GPU (handle-owned slabs), so a row costs d_model + 4 * d_model bytes over the bus instead
+ * of the d_model + 2 * d_ff (+ d_ff + 4 * d_model) of two separate *_host calls.  Scales are host values.  Blocking. */
+int sl8_mlp_chain_fp8_host(sl8_handle_t h,
+                           const void* A, int64_t lda,
+                           const void* W1, int64_t ldw1, float scale_a, float scale_w1, const void* bias1,
+                           float hidden_scale,
+                           const void* W2, int64_t ldw2, float scale_w2, const void* bias2,
+                           const void* residual, int64_t ldr,
+                           void* D, int64_t ldd,
+                           int64_t M, int d_model, int d_ff, unsigned flags);
+
 /* ---- dispatch ------------------------------------------------------------------------- */
 
 /* Variant the dispatch table selects for (op, out_dtype, M, N, K) and flags = 0; the reference has a

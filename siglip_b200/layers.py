@@ -214,6 +214,47 @@ class Engine:
             self._stream(stream)))
         return D
 
+    def mlp_chain(self, A, W1, bias1, W2, bias2, residual, *, scale_a, scale_w1, scale_w2, hidden_scale, hidden=None,
+                  out=None, flags: int = 0, stream=None) -> torch.Tensor:
+        """D = FC2(e4m3(GELU(FC1(A)) / hidden_scale)) + residual: the block's MLP as one call (sl8_mlp_chain_fp8).
+        ``hidden`` is the e4m3 scratch [M, d_ff] (uint8, row pitch a multiple of 16 bytes); allocated when None."""
+        M, d_ff, d_model = self._operands(A, W1)
+        n2, k2 = W2.shape
+        if (n2, k2) != (d_model, d_ff) or not _is_fp8(W2) or W2.stride(1) != 1:
+            raise ValueError(f"W2 must be e4m3 [{d_model}, {d_ff}] with K contiguous")
+        if residual.dtype != torch.bfloat16 or tuple(residual.shape) != (M, d_model) or residual.stride(1) != 1:
+            raise ValueError("residual must be bf16 [M, d_model] with d_model contiguous")
+        if hidden_scale is None:
+            raise ValueError("hidden_scale (device float) is required: the scale of the e4m3 hidden activations")
+        if bias1 is not None and bias1.dtype == torch.float32:
+            flags |= _l.SL8_FLAG_BIAS_F32
+        if hidden is None:
+            hidden = torch.empty((M, (d_ff + 127) // 128 * 128), dtype=torch.uint8, device=A.device)[:, :d_ff]
+        self._check_out(hidden, M, d_ff, self._E4M3_TYPES)
+        for name, t in (("W2", W2), ("bias1", bias1), ("bias2", bias2), ("residual", residual), ("scale_a", scale_a),
+                        ("scale_w1", scale_w1), ("scale_w2", scale_w2), ("hidden_scale", hidden_scale)):
+            self._on_device(name, t)
+        D = self._new_out(M, d_model, torch.bfloat16, A.device) if out is None else self._check_out(out, M, d_model, (torch.bfloat16,))
+        self._check(self._lib.sl8_mlp_chain_fp8(
+            self._h, A.data_ptr(), A.stride(0), W1.data_ptr(), W1.stride(0), _ptr(scale_a), _ptr(scale_w1), _ptr(bias1),
+            hidden.data_ptr(), hidden.stride(0), _ptr(hidden_scale), W2.data_ptr(), W2.stride(0), _ptr(scale_w2), _ptr(bias2),
+            residual.data_ptr(), residual.stride(0), D.data_ptr(), D.stride(0), M, d_model, d_ff, int(flags),
+            self._stream(stream)))
+        return D
+
+    def mlp_chain_host(self, A, W1, bias1, W2, bias2, residual, out, *, scale_a, scale_w1, scale_w2, hidden_scale, flags=0):
+        """The MLP on HOST tensors (pinned memory gives full bus speed): A and the residual go up, D comes down, the
+        hidden activations stay on the GPU (sl8_mlp_chain_fp8_host).  Blocking."""
+        M, d_model = A.shape
+        d_ff = W1.shape[0]
+        if bias1 is not None and bias1.dtype == torch.float32:
+            flags |= _l.SL8_FLAG_BIAS_F32
+        self._check(self._lib.sl8_mlp_chain_fp8_host(
+            self._h, A.data_ptr(), A.stride(0), W1.data_ptr(), W1.stride(0), float(scale_a), float(scale_w1), _ptr(bias1),
+            float(hidden_scale), W2.data_ptr(), W2.stride(0), float(scale_w2), _ptr(bias2), residual.data_ptr(),
+            residual.stride(0), out.data_ptr(), out.stride(0), M, d_model, d_ff, int(flags)))
+        return out
+
     # ------------------------------------------------------------------ producer-side steps
     @staticmethod
     def _dt(x) -> int:

@@ -69,6 +69,8 @@ SIGNATURES = {
     "sl8_patch_embed_fp8_host": (_I, [_P, _P, _I64, _P, _I64, _F, _F, _P, _I64, _I, _I, _I, _P, _I64, _I64, _I, _I, _U]),
     "sl8_fc1_gelu_fp8_host": (_I, [_P, _P, _I64, _P, _I64, _F, _F, _P, _P, _I64, _I, _F, _I64, _I, _I, _U]),
     "sl8_fc2_residual_fp8_host": (_I, [_P, _P, _I64, _P, _I64, _F, _F, _P, _P, _I64, _P, _I64, _I64, _I, _I, _U]),
+    "sl8_mlp_chain_fp8": (_I, [_P, _P, _I64, _P, _I64, _P, _P, _P, _P, _I64, _P, _P, _I64, _P, _P, _P, _I64, _P, _I64, _I64, _I, _I, _U, _P]),
+    "sl8_mlp_chain_fp8_host": (_I, [_P, _P, _I64, _P, _I64, _F, _F, _P, _F, _P, _I64, _F, _P, _P, _I64, _P, _I64, _I64, _I, _I, _U]),
     "sl8_query_config": (_I, [_P, _I, _I, _I64, _I, _I, C.POINTER(Config)]),
     "sl8_num_variants": (_I, []),
     "sl8_describe_variant": (_I, [_I, C.POINTER(Config)]),

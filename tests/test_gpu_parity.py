@@ -213,6 +213,51 @@ def test_fc1_fc2_chain_through_e4m3(engine, oracle):
     check_bf16(bits(D), d_ref, "chain: FC2 on FC1's codes")
 
 
+def test_mlp_chain_entry_points(engine, oracle):
+    """sl8_mlp_chain_fp8 (device operands) and sl8_mlp_chain_fp8_host (host operands, slabs on three streams, the
+    hidden activations never leaving the GPU): the hidden codes against the oracle's FC1, D against the oracle's FC2
+    run on those very codes, and the host form bit-identical to the device form on 25 000 rows (three slabs of 11 520 rows:
+    64 MiB of A + residual + D each)."""
+    import siglip_b200.lib as L
+    M, D_MODEL, D_FF = 1500, 1152, 4304
+    p1 = synth.make_fc1(M, D_FF, D_MODEL, seed=41, device=DEV)
+    p2 = synth.make_fc2(M, D_MODEL, D_FF, seed=42, device=DEV)
+    h_scale = 0.0125
+    H = torch.zeros((M, synth.pitch128(D_FF)), dtype=torch.uint8, device=DEV)[:, :D_FF]
+    D = engine.mlp_chain(p1.A, p1.B, p1.bias, p2.B, p2.bias, p2.residual, scale_a=dscalar(p1.scale_a),
+                         scale_w1=dscalar(p1.scale_b), scale_w2=dscalar(p2.scale_b), hidden_scale=dscalar(h_scale), hidden=H)
+    engine.device_status()
+    h_ref = oracle.fc1_gelu(p1.A.cpu().numpy(), p1.B.cpu().numpy(), p1.scale_a, p1.scale_b, bits(p1.bias),
+                            out_e4m3=True, out_scale=h_scale)
+    check_e4m3(H.cpu().numpy(), h_ref, "mlp chain: hidden codes")
+    d_ref = oracle.fc2_residual(H.cpu().numpy(), p2.B.cpu().numpy(), h_scale, p2.scale_b, bits(p2.bias), bits(p2.residual))
+    check_bf16(bits(D), d_ref, "mlp chain: D on the hidden codes")
+    # the hidden scale is not optional: the codes mean nothing without it
+    rc = engine._lib.sl8_mlp_chain_fp8(
+        engine._h, p1.A.data_ptr(), p1.A.stride(0), p1.B.data_ptr(), p1.B.stride(0), None, None, None, H.data_ptr(),
+        H.stride(0), None, p2.B.data_ptr(), p2.B.stride(0), None, None, p2.residual.data_ptr(), p2.residual.stride(0),
+        D.data_ptr(), D.stride(0), M, D_MODEL, D_FF, 0, None)
+    assert rc == L.SL8_ERR_INVALID_VALUE
+
+    # host operands, several slabs
+    Mh = 25000
+    q1 = synth.make_fc1(Mh, D_FF, D_MODEL, seed=43, device=DEV)
+    res = (torch.randn((Mh, D_MODEL), generator=torch.Generator(device=DEV).manual_seed(44), device=DEV)).to(torch.bfloat16)
+    Dd = engine.mlp_chain(q1.A, q1.B, q1.bias, p2.B, p2.bias, res, scale_a=dscalar(q1.scale_a), scale_w1=dscalar(q1.scale_b),
+                          scale_w2=dscalar(p2.scale_b), hidden_scale=dscalar(h_scale))
+    engine.device_status()
+    A_h = torch.zeros((Mh, q1.A.stride(0)), dtype=torch.uint8).pin_memory()[:, :D_MODEL]
+    A_h.copy_(q1.A)
+    W1_h = torch.zeros((D_FF, q1.B.stride(0)), dtype=torch.uint8)[:, :D_MODEL]
+    W1_h.copy_(q1.B)
+    W2_h = torch.zeros((D_MODEL, p2.B.stride(0)), dtype=torch.uint8)[:, :D_FF]
+    W2_h.copy_(p2.B)
+    D_h = torch.empty((Mh, D_MODEL), dtype=torch.bfloat16).pin_memory()
+    engine.mlp_chain_host(A_h, W1_h, q1.bias.cpu(), W2_h, p2.bias.cpu(), res.cpu().pin_memory(), D_h,
+                          scale_a=q1.scale_a, scale_w1=q1.scale_b, scale_w2=p2.scale_b, hidden_scale=h_scale)
+    assert torch.equal(D_h.view(torch.uint16), Dd.cpu().view(torch.uint16)), "host chain differs from the device chain"
+
+
 def test_multi_wave_determinism(engine, oracle):
     """More tiles than SMs (several rounds of the persistent loop and both TMEM buffers), twice: bit-equal runs."""
     p = synth.make_fc1(6000, 2304, 1152, seed=3, device=DEV)
