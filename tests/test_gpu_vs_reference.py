@@ -3,8 +3,9 @@
 `make -C oracle ref` compiles the reference's three layer sources (from where they lie) into
 oracle/_ref/libsl8_ref_{pe,fc1,fc2}.so behind a small launch shim (oracle/ref_shim.cu).  The
 reference is shaped at compile time: M = 928 256 rows and its SigLIP-B/16 N, K, operands consumed as
-raw e4m3 codes (scale 1), fp32 bias, a 32x32-blocked bf16 bias+pos table.  Each test feeds both
-implementations the same random codes at exactly that shape, compares the outputs, arbitrates on a
+raw e4m3 codes (scale 1), fp32 bias, a 32x32-blocked bf16 bias+pos table.  `make -C oracle ref_so400m` compiles
+the same sources for the zero-padded SigLIP-So400m shapes (libsl8_ref_*_so400m.so).  Each test feeds both
+implementations the same random codes at exactly that shape (this library on the unpadded views), compares the outputs, arbitrates on a
 row sample with the CPU oracle, prints both kernels' times (CUDA events) and appends them to
 ref_compare.txt in the directory SL8_REPORT_DIR names, when it is set.
 
@@ -84,6 +85,7 @@ def compare(name, D_ref, D_new, oracle_rows_fn, M, N, K, t_ref, t_new):
     lane group (warp - 2) % 4 (kernel_body.cuh:640-641,66) while the hardware gives warp w the lanes of
     group w % 4, which swaps the 32-row groups of every 128-row block in pairs; its constant-row self-test
     cannot see that."""
+    D_ref = D_ref.contiguous()
     same = (D_ref.view(torch.uint16) == D_new.view(torch.uint16))
     exact = float(same.float().mean())
     flops = 2.0 * M * N * K
@@ -106,73 +108,107 @@ def compare(name, D_ref, D_new, oracle_rows_fn, M, N, K, t_ref, t_new):
     return "row-permuted"
 
 
-def test_patch_embed_vs_reference(engine, oracle):
-    lib, M, N, K, period, table_rows = load_ref("pe")
+# Shapes the reference is compiled for -> the shape the two libraries are compared on.  The So400m builds
+# (`make -C oracle ref_so400m`) are compiled for zero-padded shapes (N to a multiple of 256, K to a multiple of 128, M to
+# a multiple of 256): the reference runs on the padded operands, this library on the unpadded views of the SAME buffers.
+# (compare() looks operand rows r ^ 64 up as well: near the end of M those lie in the zero padding, so the oracle is
+# fed from the padded buffers.)
+TRUE_SHAPE = {"pe_so400m": (186624, 1152, 588), "fc1_so400m": (46656, 4304, 1152), "fc2_so400m": (46656, 1152, 4304)}
+
+
+def padded_codes(rows_p, cols_p, rows, cols, std, seed):
+    """[rows_p, cols_p] e4m3 codes, N(0, std) in the leading [rows, cols] block and zero elsewhere."""
+    out = torch.zeros((rows_p, cols_p), dtype=torch.uint8, device=DEV)
+    out[:rows, :cols] = raw_codes(rows, cols, std, seed)
+    return out
+
+
+@pytest.mark.parametrize("build", ["pe", "pe_so400m"])
+def test_patch_embed_vs_reference(engine, oracle, build):
+    lib, Mp, Np, Kp, period, table_rows = load_ref(build)
+    M, N, K = TRUE_SHAPE.get(build, (Mp, Np, Kp))
     lib.sl8_ref_make_table.argtypes = [C.c_void_p] * 4
     lib.sl8_ref_make_table.restype = C.c_int
-    A, B = raw_codes(M, K, 1.0, 1), raw_codes(N, K, 0.02, 2)
+    Ap, Bp = padded_codes(Mp, Kp, M, K, 1.0, 1), padded_codes(Np, Kp, N, K, 0.02, 2)
+    A, B = Ap[:M, :K], Bp[:N, :K]
     g = torch.Generator(device=DEV).manual_seed(3)
-    bias = torch.randn((N,), generator=g, device=DEV) * 0.01
-    pos = torch.randn((period, N), generator=g, device=DEV) * 0.02
-    blocked = torch.zeros((table_rows * N,), dtype=torch.bfloat16, device=DEV)
-    assert lib.sl8_ref_make_table(bias.data_ptr(), pos.data_ptr(), blocked.data_ptr(), None) == 0
+    bias_p = torch.zeros((Np,), device=DEV)
+    bias_p[:N] = torch.randn((N,), generator=g, device=DEV) * 0.01
+    pos_p = torch.zeros((period, Np), device=DEV)
+    pos_p[:, :N] = torch.randn((period, N), generator=g, device=DEV) * 0.02
+    blocked = torch.zeros((table_rows * Np,), dtype=torch.bfloat16, device=DEV)
+    assert lib.sl8_ref_make_table(bias_p.data_ptr(), pos_p.data_ptr(), blocked.data_ptr(), None) == 0
+    bias, pos = bias_p[:N].contiguous(), pos_p[:, :N].contiguous()
     table = engine.make_table(bias, pos)                                   # same arithmetic, row-major, padded
     assert torch.equal(table[:period], (bias[None, :] + pos).to(torch.bfloat16))
-    D_ref = torch.zeros((M, N), dtype=torch.bfloat16, device=DEV)
+    D_ref = torch.zeros((Mp, Np), dtype=torch.bfloat16, device=DEV)
     D_new = torch.zeros((M, N), dtype=torch.bfloat16, device=DEV)
-    run_ref = lambda: lib.sl8_ref_launch(A.data_ptr(), B.data_ptr(), blocked.data_ptr(), D_ref.data_ptr(), None, None)
+    run_ref = lambda: lib.sl8_ref_launch(Ap.data_ptr(), Bp.data_ptr(), blocked.data_ptr(), D_ref.data_ptr(), None, None)
     run_new = lambda: engine.patch_embed(A, B, table, period=period, out=D_new)
     assert run_ref() == 0
     run_new()
     engine.device_status()
     t_ref, t_new = time_ms(run_ref), time_ms(run_new)
-    Bn, tn = B.cpu().numpy(), table[:period].contiguous().view(torch.uint16).cpu().numpy()
+    Bn, tn = B.contiguous().cpu().numpy(), table[:period].contiguous().view(torch.uint16).cpu().numpy()
 
     def orc(rows, a_rows):
         out = np.empty((len(rows), N), dtype=np.uint16)
         for i, (r, a) in enumerate(zip(rows, a_rows)):          # one row at a time keeps each row's table phase right
-            out[i] = oracle.patch_embed(A[a:a + 1].cpu().numpy(), Bn, 1.0, 1.0, tn, row_phase=int(r % period))[0]
+            out[i] = oracle.patch_embed(Ap[a:a + 1, :K].contiguous().cpu().numpy(), Bn, 1.0, 1.0, tn, row_phase=int(r % period))[0]
         return out
 
-    assert compare("patch-embed", D_ref, D_new, orc, M, N, K, t_ref, t_new) in ("matches", "row-permuted")
+    assert compare(f"patch-embed [{build}]", D_ref[:M, :N], D_new, orc, M, N, K, t_ref, t_new) in ("matches", "row-permuted")
 
 
-def test_fc1_vs_reference(engine, oracle):
-    lib, M, N, K, _, _ = load_ref("fc1")
-    A, B = raw_codes(M, K, 1.0, 4), raw_codes(N, K, 0.02, 5)
+@pytest.mark.parametrize("build", ["fc1", "fc1_so400m"])
+def test_fc1_vs_reference(engine, oracle, build):
+    lib, Mp, Np, Kp, _, _ = load_ref(build)
+    M, N, K = TRUE_SHAPE.get(build, (Mp, Np, Kp))
+    Ap, Bp = padded_codes(Mp, Kp, M, K, 1.0, 4), padded_codes(Np, Kp, N, K, 0.02, 5)
+    A, B = Ap[:M, :K], Bp[:N, :K]
     g = torch.Generator(device=DEV).manual_seed(6)
-    bias = torch.randn((N,), generator=g, device=DEV) * 0.01
-    D_ref = torch.zeros((M, N), dtype=torch.bfloat16, device=DEV)
+    bias_p = torch.zeros((Np,), device=DEV)
+    bias_p[:N] = torch.randn((N,), generator=g, device=DEV) * 0.01
+    bias = bias_p[:N]
+    D_ref = torch.zeros((Mp, Np), dtype=torch.bfloat16, device=DEV)
     D_new = torch.zeros((M, N), dtype=torch.bfloat16, device=DEV)
-    run_ref = lambda: lib.sl8_ref_launch(A.data_ptr(), B.data_ptr(), bias.data_ptr(), D_ref.data_ptr(), None, None)
+    run_ref = lambda: lib.sl8_ref_launch(Ap.data_ptr(), Bp.data_ptr(), bias_p.data_ptr(), D_ref.data_ptr(), None, None)
     run_new = lambda: engine.fc1_gelu(A, B, bias, out=D_new)
     assert run_ref() == 0
     run_new()
     engine.device_status()
     t_ref, t_new = time_ms(run_ref, 5), time_ms(run_new, 5)
-    Bn, bn = B.cpu().numpy(), bias.cpu().numpy()
-    orc = lambda rows, a_rows: oracle.fc1_gelu(A[torch.as_tensor(a_rows, device=DEV)].cpu().numpy(), Bn, 1.0, 1.0, bn, flags=1)
-    assert compare("FC1+GELU", D_ref, D_new, orc, M, N, K, t_ref, t_new) in ("matches", "row-permuted")
+    Bn, bn = B.contiguous().cpu().numpy(), bias.cpu().numpy()
+    orc = lambda rows, a_rows: oracle.fc1_gelu(Ap[torch.as_tensor(a_rows, device=DEV)][:, :K].contiguous().cpu().numpy(), Bn, 1.0, 1.0, bn, flags=1)
+    assert compare(f"FC1+GELU [{build}]", D_ref[:M, :N], D_new, orc, M, N, K, t_ref, t_new) in ("matches", "row-permuted")
 
 
-def test_fc2_vs_reference(engine, oracle):
-    lib, M, N, K, _, _ = load_ref("fc2")
-    A, B = raw_codes(M, K, 0.5, 7), raw_codes(N, K, 0.02, 8)
+@pytest.mark.parametrize("build", ["fc2", "fc2_so400m"])
+def test_fc2_vs_reference(engine, oracle, build):
+    lib, Mp, Np, Kp, _, _ = load_ref(build)
+    M, N, K = TRUE_SHAPE.get(build, (Mp, Np, Kp))
+    Ap, Bp = padded_codes(Mp, Kp, M, K, 0.5, 7), padded_codes(Np, Kp, N, K, 0.02, 8)
+    A, B = Ap[:M, :K], Bp[:N, :K]
     g = torch.Generator(device=DEV).manual_seed(9)
-    bias = torch.randn((N,), generator=g, device=DEV) * 0.01
-    residual = torch.randn((M, N), generator=g, device=DEV).to(torch.bfloat16)
-    D_ref = torch.zeros((M, N), dtype=torch.bfloat16, device=DEV)
+    bias_p = torch.zeros((Np,), device=DEV)
+    bias_p[:N] = torch.randn((N,), generator=g, device=DEV) * 0.01
+    bias = bias_p[:N]
+    res_p = torch.zeros((Mp, Np), dtype=torch.bfloat16, device=DEV)
+    res_p[:M, :N] = torch.randn((M, N), generator=g, device=DEV).to(torch.bfloat16)
+    residual = res_p[:M, :N]
+    D_ref = torch.zeros((Mp, Np), dtype=torch.bfloat16, device=DEV)
     D_new = torch.zeros((M, N), dtype=torch.bfloat16, device=DEV)
-    run_ref = lambda: lib.sl8_ref_launch(A.data_ptr(), B.data_ptr(), bias.data_ptr(), D_ref.data_ptr(), residual.data_ptr(), None)
+    run_ref = lambda: lib.sl8_ref_launch(Ap.data_ptr(), Bp.data_ptr(), bias_p.data_ptr(), D_ref.data_ptr(), res_p.data_ptr(), None)
     run_new = lambda: engine.fc2_residual(A, B, bias, residual, out=D_new)
     assert run_ref() == 0
     run_new()
     engine.device_status()
     t_ref, t_new = time_ms(run_ref, 5), time_ms(run_new, 5)
-    Bn, bn = B.cpu().numpy(), bias.cpu().numpy()
+    Bn, bn = B.contiguous().cpu().numpy(), bias.cpu().numpy()
 
     def orc(rows, a_rows):
         idx, aidx = torch.as_tensor(rows, device=DEV), torch.as_tensor(a_rows, device=DEV)
-        return oracle.fc2_residual(A[aidx].cpu().numpy(), Bn, 1.0, 1.0, bn, residual[idx].view(torch.uint16).cpu().numpy(), flags=1)
+        return oracle.fc2_residual(Ap[aidx][:, :K].contiguous().cpu().numpy(), Bn, 1.0, 1.0, bn,
+                                   residual[idx].contiguous().view(torch.uint16).cpu().numpy(), flags=1)
 
-    assert compare("FC2+residual", D_ref, D_new, orc, M, N, K, t_ref, t_new) in ("matches", "row-permuted")
+    assert compare(f"FC2+residual [{build}]", D_ref[:M, :N], D_new, orc, M, N, K, t_ref, t_new) in ("matches", "row-permuted")
