@@ -321,10 +321,45 @@ def cublaslt_baseline(p, dev, steps: int) -> dict:
             full = lambda i=0: gemm().view(imgs, p.period, p.N).add_(p.table)
         t_gemm = time_steps(gemm, steps, 3, lambda: None)
         t_full = time_steps(full, steps, 3, lambda: None)
-        return {"cublaslt_gemm_ms": t_gemm, "cublaslt_gemm_tflops": p.flops() / t_gemm / 1e9,
-                "cublaslt_unfused_ms": t_full, "cublaslt_unfused_tflops": p.flops() / t_full / 1e9}
+        return {"torch_scaled_mm_gemm_ms": t_gemm, "torch_scaled_mm_gemm_tflops": p.flops() / t_gemm / 1e9,
+                "torch_scaled_mm_plus_epilogue_kernels_ms": t_full}
     except Exception as e:          # a torch build without _scaled_mm for this shape: report, do not fail the bench
-        return {"cublaslt_error": f"{type(e).__name__}: {str(e)[:160]}"}
+        return {"torch_scaled_mm_error": f"{type(e).__name__}: {str(e)[:160]}"}
+
+
+def host_baselines(name: str, runs: int = 20) -> dict:
+    """cuBLASLt FP8 and the reference's own kernels on the configuration's shape, timed by the C++ bench host
+    (siglip_b200/lib/siglip_bench) on seeded random codes: cuBLASLt through cublasLtMatmul with per-tensor scale pointers,
+    the best of its heuristics, bare and with the layer's epilogue fused (GELU_BIAS; BIAS + residual as C with beta = 1;
+    the table tiled to M rows as C with beta = 1); the reference kernels through oracle/_ref (baseline code, never on
+    the product path; the column is left out where that build is absent)."""
+    import subprocess
+    exe = ROOT / "siglip_b200" / "lib" / "siglip_bench"
+    out = {}
+    if not exe.exists():
+        return {"host_baselines_error": f"{exe} not built"}
+
+    def run(impl):
+        try:
+            r = subprocess.run([str(exe), "--config", name, "--data", "random", "--impl", impl, "--runs", str(runs)],
+                               capture_output=True, text=True, timeout=300)
+            lines = [l for l in r.stdout.splitlines() if l.startswith("{")]
+            return json.loads(lines[-1]) if r.returncode == 0 and lines else None
+        except Exception:
+            return None
+
+    lt = run("cublaslt")
+    if lt:
+        out.update({"cublaslt_gemm_ms": lt["gemm_ms"], "cublaslt_fused_ms": lt["fused_ms"], "cublaslt_fused": lt["fused"],
+                    "cublaslt_heuristics_tried": lt["gemm_heuristics"], "cublaslt_fused_vs_this_library_max_rel_diff": lt["max_rel_diff_vs_new"]})
+    else:
+        out["cublaslt_error"] = "siglip_bench --impl cublaslt failed"
+    so = {"C1": "pe", "C2": "fc1_so400m", "C3": "fc2_so400m", "C4": "pe_so400m"}[name]
+    if (ROOT / "oracle" / "_ref" / f"libsl8_ref_{so}.so").exists() and name != "C1":      # the B/16 build is shaped for 928 256 rows
+        rf = run("ref")
+        if rf:
+            out.update({"reference_ms": rf["ms"], "reference_build": f"oracle/_ref/libsl8_ref_{so}.so (zero-padded shape)"})
+    return out
 
 
 def roofline_of(p, ms: float, peaks: dict, traffic=None) -> dict:
@@ -345,7 +380,7 @@ def roofline_of(p, ms: float, peaks: dict, traffic=None) -> dict:
             "frac_of_nominal_4500": tf / 4500.0, "hbm_gbs_algorithmic": gbs}
 
 
-def layer_table(eng, dev, launches: int, peaks: dict, names=("C1", "C3", "C4")) -> dict:
+def layer_table(eng, dev, launches: int, peaks: dict, names=("C1", "C3", "C4"), host: bool = True) -> dict:
     """The other configurations, timed launch by launch (an event pair per launch, three rotating operand sets,
     3 warm-up launches), each beside cuBLASLt's FP8 GEMM on the same operands."""
     from siglip_b200 import synth
@@ -362,12 +397,16 @@ def layer_table(eng, dev, launches: int, peaks: dict, names=("C1", "C3", "C4")) 
                     "roofline": roofline_of(p, ms, peaks),
                     "kernel_config": eng.query_config(p.op, p.M, p.N, p.K),
                     "workload": workload_config(name)["workload"]})
+        fn2 = fn
         del fn
-        torch.cuda.empty_cache()
+        row["ms_back_to_back"] = time_steps(fn2, launches, 3, lambda: None)      # no events between the launches
+        del fn2
         row.update(cublaslt_baseline(p, dev, launches))
         out[name] = row
         del p
         torch.cuda.empty_cache()
+    for name in names if host else ():     # the C++ host's arms run as child processes (on GPU 0: rank 0 only)
+        out[name].update(host_baselines(name))
     return out
 
 
@@ -672,9 +711,11 @@ def main() -> None:
                                     "seconds": secs}
         if chain:
             line["chain"] = chain
+        if not args.no_layers and args.config in ("C1", "C2", "C3", "C4"):
+            line["baselines"] = host_baselines(args.config)
     if not args.no_layers:
         # every rank runs the table on its own GPU (the ranks stay in step); rank 0 reports its own
-        tab = layer_table(eng, dev, max(20, min(args.steps, 100)), peaks, tuple(n for n in args.layer_names.split(",") if n))
+        tab = layer_table(eng, dev, max(20, min(args.steps, 100)), peaks, tuple(n for n in args.layer_names.split(",") if n), host=(rank == 0))
         if rank == 0:
             line["layers"] = tab
     if args.prep and rank == 0:

@@ -93,7 +93,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if res.returncode != 0:
         raise RuntimeError(f"link failed: {' '.join(link)}\n{res.stdout}\n{res.stderr}")
     bench = [exe, *ARCH_FLAGS, "-O3", "-std=c++17", "-lineinfo", str(CSRC / "sl8_bench.cu"), "-o", str(BENCH),
-             f"-L{LIB.parent}", "-lsiglip_fp8", "-Xlinker", "-rpath=$ORIGIN", "-cudart", "static"]
+             f"-L{LIB.parent}", "-lsiglip_fp8", "-lcublasLt", "-ldl", "-Xlinker", "-rpath=$ORIGIN", "-cudart", "static"]
     res = subprocess.run(bench, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"bench host build failed: {' '.join(bench)}\n{res.stdout}\n{res.stderr}")

@@ -1,27 +1,51 @@
 // sl8_bench.cu -- per-layer bench host over the C ABI, speaking the reference harness's protocol.
 //
 // Counterpart of the reference's three bench hosts (patch_embed.cu:104-346, fc1_gelu.cu:52-254,
-// fc2.cu:72-289): same constant operands (A = 0x3C, B rows alternating 0x3C / 0x38, bias[c] = c + 1,
-// pos[r, c] = 3 (r + 1), residual[r, c] = bf16((r % 128) / 4 + c / 8)), same 2 warm-up + 10 timed launches
-// under one event pair, same 32 closed-form spot checks and 1024-sample strided checksum, and the same
-// machine-readable line its drivers parse (tools/grid_search.py:153-158, tools/compare_all.py:90-100):
+// fc2.cu:72-289) and of its cuBLASLt bench (bench/cublas_bench.cu).  The default run reproduces the reference
+// harness: constant operands (A = 0x3C, B rows alternating 0x3C / 0x38, bias[c] = c + 1, pos[r, c] = 3 (r + 1),
+// residual[r, c] = bf16((r % 128) / 4 + c / 8)), 2 warm-up + 10 timed launches under one event pair, 32 closed-form
+// spot checks, a 1024-sample strided checksum, and the machine-readable line its drivers parse
+// (tools/grid_search.py:153-158, tools/compare_all.py:90-100):
 //
 //     @@RESULT ms=%.3f tflops=%.2f checksum=%f valid=%d c0=%.1f
 //
-// plus "Custom kernel: %.3f ms" for tools/stat_test.py:27.  Shapes are run-time here:
+// plus "Custom kernel: %.3f ms" for tools/stat_test.py:27, followed by one JSON line.  Shapes are run-time:
 //
 //     siglip_bench --layer pe|fc1|fc2 [--M rows] [--N n] [--K k] [--period p] [--runs r]
-//     siglip_bench --config C1|C2|C3|C4            (the benchmark configurations: layer and shape in one word)
+//     siglip_bench --config C1|C2|C3|C4|C5      (the benchmark configurations; C5 = --op chain on 1024 images)
+//     siglip_bench --op chain --M rows          (FC1 + GELU -> e4m3 -> FC2 + residual, d_model 1152, d_ff 4304)
 //
-// Defaults are the reference's: M = 928256, patch-embed 768 x 768 period 196, FC1 3072 x 768, FC2 768 x 3072.
-// A JSON line with the same figures follows the @@RESULT line.
+// Beyond the reference harness:
+//     --impl new        this library (default)
+//     --impl cublaslt   cublasLtMatmul on the same operands, per-tensor scale pointers, the best of the returned
+//                       heuristics (up to 128, 256 MiB workspace: bench/cublas_bench.cu:163-203), bare GEMM and the
+//                       fused epilogue the layer maps to: GELU_BIAS (FC1), BIAS with the residual as C and beta = 1
+//                       (FC2), beta = 1 with the table tiled to M rows as C (patch-embed) -- bench/cublas_bench.cu:369-402
+//     --impl ref        the reference's own kernels through oracle/_ref/libsl8_ref_<layer>[_so400m].so (built by
+//                       `make -C oracle ref ref_so400m` from the reference checkout; their shapes are compile-time)
+//     --impl cpu        the CPU restatement (oracle/libsl8_oracle.so), on a bounded number of rows
+//     --data random     seeded pseudo-random e4m3 codes instead of the constants (constant operands toggle few bits,
+//                       draw little power and so run at a clock real data never sees); validation then compares with
+//                       --impl new instead of the closed forms
+//     --gpus n          the same problem on n GPUs at once, one handle and one host thread per GPU, rows divided by
+//                       image (729 rows); the time is the slowest GPU's
+//     --sustain s       additionally run back to back for s seconds and report that rate
+// Every launch is timed by its own event pair as well: min / median / mean over the runs.
+#include <cublasLt.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <dlfcn.h>
 
+#include <unistd.h>
+
+#include <algorithm>
+#include <chrono>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <string>
+#include <thread>
 #include <vector>
 
 #include "../../include/siglip_fp8.h"
@@ -44,7 +68,18 @@
         }                                                                                         \
     } while (0)
 
-static __global__ void fill_residual(__nv_bfloat16* res, int n, long long total) {
+#define CHECK_LT(x)                                                                               \
+    do {                                                                                          \
+        cublasStatus_t s_ = (x);                                                                  \
+        if (s_ != CUBLAS_STATUS_SUCCESS) {                                                        \
+            fprintf(stderr, "cuBLASLt %s:%d: status %d\n", __FILE__, __LINE__, (int)s_);          \
+            return 1;                                                                             \
+        }                                                                                         \
+    } while (0)
+
+namespace {
+
+__global__ void fill_residual(__nv_bfloat16* res, int n, long long total) {
     const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx < total) {
         const int col = static_cast<int>(idx % n);
@@ -53,157 +88,603 @@ static __global__ void fill_residual(__nv_bfloat16* res, int n, long long total)
     }
 }
 
-static float gelu_host(float x) {   // fc1_gelu.cu:16-19
+// Seeded pseudo-random e4m3 codes: sign, exponent field 0 .. max_exp, 3 mantissa bits (|value| < 2^(max_exp - 6)), columns
+// >= cols of each row left zero.
+__global__ void fill_random_codes(uint8_t* p, long long rows, int cols, long long pitch, unsigned seed, int max_exp) {
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= rows * pitch) return;
+    const int c = static_cast<int>(idx % pitch);
+    unsigned h = static_cast<unsigned>(idx) * 2654435761u ^ (static_cast<unsigned>(idx >> 32) + seed) * 40503u;
+    h ^= h >> 15; h *= 2246822519u; h ^= h >> 13; h *= 3266489917u; h ^= h >> 16;
+    const unsigned mag = (h >> 8) % static_cast<unsigned>((max_exp + 1) * 8);
+    p[idx] = c < cols ? static_cast<uint8_t>((h & 0x80u) | mag) : 0;
+}
+
+__global__ void fill_random_bf16(__nv_bfloat16* p, long long total, unsigned seed, float scale) {
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    unsigned h = static_cast<unsigned>(idx) * 2654435761u ^ (static_cast<unsigned>(idx >> 32) + seed) * 40503u;
+    h ^= h >> 15; h *= 2246822519u; h ^= h >> 13;
+    p[idx] = __float2bfloat16((static_cast<float>(h & 0xFFFF) / 32768.0f - 1.0f) * scale);
+}
+
+// out[r, :] = table[r % period, :]: the table tiled to M rows, the C operand of cuBLASLt's beta = 1 form.
+__global__ void tile_table(const __nv_bfloat16* table, int period, int n, __nv_bfloat16* out, long long total) {
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx < total) out[idx] = table[(idx / n) % period * n + idx % n];
+}
+
+__global__ void f32_to_bf16(const float* in, __nv_bfloat16* out, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = __float2bfloat16(in[i]);
+}
+
+float gelu_host(float x) {   // fc1_gelu.cu:16-19
     const float k = 0.7978845608f;
     return 0.5f * x * (1.0f + tanhf(k * (x + 0.044715f * x * x * x)));
 }
 
-static float bf16_round(float x) { return __bfloat162float(__float2bfloat16(x)); }
+float bf16_round(float x) { return __bfloat162float(__float2bfloat16(x)); }
 
-int main(int argc, char** argv) {
-    setbuf(stdout, NULL);
-    const char* layer = "pe";
-    long long M = 928256;
-    int N = -1, K = -1, period = 196, runs = 10;
-    for (int i = 1; i < argc; i++) {
-        if (!strcmp(argv[i], "--layer") && i + 1 < argc) layer = argv[++i];
-        else if (!strcmp(argv[i], "--M") && i + 1 < argc) M = atoll(argv[++i]);
-        else if (!strcmp(argv[i], "--N") && i + 1 < argc) N = atoi(argv[++i]);
-        else if (!strcmp(argv[i], "--K") && i + 1 < argc) K = atoi(argv[++i]);
-        else if (!strcmp(argv[i], "--period") && i + 1 < argc) period = atoi(argv[++i]);
-        else if (!strcmp(argv[i], "--runs") && i + 1 < argc) runs = atoi(argv[++i]);
-        else if (!strcmp(argv[i], "--config") && i + 1 < argc) {
-            const char* c = argv[++i];
-            if (!strcmp(c, "C1")) { layer = "pe"; M = 6272; N = 768; K = 768; period = 196; }
-            else if (!strcmp(c, "C2")) { layer = "fc1"; M = 46656; N = 4304; K = 1152; }
-            else if (!strcmp(c, "C3")) { layer = "fc2"; M = 46656; N = 1152; K = 4304; }
-            else if (!strcmp(c, "C4")) { layer = "pe"; M = 186624; N = 1152; K = 588; period = 729; }
-            else { fprintf(stderr, "unknown config %s (C1..C4)\n", c); return 2; }
-        }
-        else {
-            fprintf(stderr, "usage: %s [--config C1|C2|C3|C4] [--layer pe|fc1|fc2] [--M rows] [--N n] [--K k] [--period p] [--runs r]\n", argv[0]);
-            return 2;
-        }
-    }
-    const int op = !strcmp(layer, "pe") ? SL8_OP_PATCH_EMBED : !strcmp(layer, "fc1") ? SL8_OP_FC1_GELU : !strcmp(layer, "fc2") ? SL8_OP_FC2_RESIDUAL : -1;
-    if (op < 0) { fprintf(stderr, "unknown layer %s\n", layer); return 2; }
-    if (N < 0) N = op == SL8_OP_FC1_GELU ? 3072 : 768;
-    if (K < 0) K = op == SL8_OP_FC2_RESIDUAL ? 3072 : 768;
-    const long long lda = (K + 127) / 128 * 128;      // rows start on 128-byte lines
+struct Stats { double total_ms = 0, min_ms = 0, median_ms = 0, mean_ms = 0; };
 
-    sl8_handle_t h = NULL;
-    if (sl8_create(&h, 0) != SL8_OK) { fprintf(stderr, "sl8_create: %s\n", sl8_last_error_string(NULL)); return 1; }
-    sl8_config cfg;
-    CHECK_SL8(h, sl8_query_config(h, op, SL8_OUT_BF16, M, N, K, &cfg));
-    printf("%s GEMM -- %s, [%lld,%d] x [%d,%d]^T, tile %dx%dx%d, cta_group::%d, %d stages, %d epilogue warps, grid %d\n",
-           layer, sl8_version(), M, K, N, K, cfg.tile_m, cfg.tile_n, cfg.tile_k, cfg.cta_group, cfg.stages, cfg.epi_warps, cfg.grid);
-
-    // ---- operands: the reference's constant test vectors (patch_embed.cu:121-145, fc2.cu:59-66)
-    uint8_t *d_A, *d_B;
-    __nv_bfloat16 *d_C, *d_table = NULL, *d_res = NULL;
-    float *d_bias, *d_pos = NULL;
-    CHECK_CUDA(cudaMalloc(&d_A, static_cast<size_t>(M) * lda));
-    CHECK_CUDA(cudaMalloc(&d_B, static_cast<size_t>(N) * lda));
-    CHECK_CUDA(cudaMalloc(&d_bias, static_cast<size_t>(N) * sizeof(float)));
-    CHECK_CUDA(cudaMalloc(&d_C, static_cast<size_t>(M) * N * sizeof(__nv_bfloat16)));
-    CHECK_CUDA(cudaMemset(d_A, 0x3C, static_cast<size_t>(M) * lda));                     // 1.5
-    {
-        std::vector<uint8_t> hB(static_cast<size_t>(N) * lda, 0);
-        for (int n = 0; n < N; n++) memset(hB.data() + static_cast<size_t>(n) * lda, (n & 1) ? 0x38 : 0x3C, K);   // 1.0 / 1.5
-        CHECK_CUDA(cudaMemcpy(d_B, hB.data(), hB.size(), cudaMemcpyHostToDevice));
-        std::vector<float> hb(N);
-        for (int c = 0; c < N; c++) hb[c] = static_cast<float>(c + 1);
-        CHECK_CUDA(cudaMemcpy(d_bias, hb.data(), N * sizeof(float), cudaMemcpyHostToDevice));
-    }
-    int table_rows = 0;
-    if (op == SL8_OP_PATCH_EMBED) {
-        std::vector<float> hp(static_cast<size_t>(period) * N);
-        for (int r = 0; r < period; r++)
-            for (int c = 0; c < N; c++) hp[static_cast<size_t>(r) * N + c] = 3.0f * static_cast<float>(r + 1);
-        CHECK_CUDA(cudaMalloc(&d_pos, hp.size() * sizeof(float)));
-        CHECK_CUDA(cudaMemcpy(d_pos, hp.data(), hp.size() * sizeof(float), cudaMemcpyHostToDevice));
-        table_rows = sl8_padded_table_rows(period);
-        CHECK_CUDA(cudaMalloc(&d_table, static_cast<size_t>(table_rows) * N * sizeof(__nv_bfloat16)));
-        CHECK_SL8(h, sl8_make_periodic_table(h, d_bias, d_pos, period, N, d_table, N, table_rows, 0));   // precompute_combined
-    }
-    if (op == SL8_OP_FC2_RESIDUAL) {
-        const long long total = M * N;
-        CHECK_CUDA(cudaMalloc(&d_res, static_cast<size_t>(total) * sizeof(__nv_bfloat16)));
-        fill_residual<<<static_cast<unsigned>((total + 255) / 256), 256>>>(d_res, N, total);
-        CHECK_CUDA(cudaGetLastError());
-    }
-    CHECK_CUDA(cudaDeviceSynchronize());
-    printf("  Alloc + init done\n");
-
-    auto launch = [&]() -> int {
-        if (op == SL8_OP_PATCH_EMBED)
-            return sl8_patch_embed_fp8(h, d_A, lda, d_B, lda, NULL, NULL, d_table, N, period, table_rows, 0, d_C, N, M, N, K, 0, 0);
-        if (op == SL8_OP_FC1_GELU)
-            return sl8_fc1_gelu_fp8(h, d_A, lda, d_B, lda, NULL, NULL, d_bias, d_C, N, SL8_OUT_BF16, NULL, M, N, K, SL8_FLAG_BIAS_F32, 0);
-        return sl8_fc2_residual_fp8(h, d_A, lda, d_B, lda, NULL, NULL, d_bias, d_res, N, d_C, N, M, N, K, SL8_FLAG_BIAS_F32, 0);
-    };
-
-    // ---- 2 warm-up + `runs` timed launches under one event pair (patch_embed.cu:213-246)
-    for (int i = 0; i < 2; i++) CHECK_SL8(h, launch());
+// 2 warm-up launches, then `runs` launches under one event pair (the reference protocol, patch_embed.cu:213-246),
+// then `runs` more, each between its own pair of events.
+template <typename F>
+int time_launches(F&& launch, int runs, Stats* st) {
+    for (int i = 0; i < 2; i++) if (launch()) return 1;
     CHECK_CUDA(cudaDeviceSynchronize());
     cudaEvent_t e0, e1;
     CHECK_CUDA(cudaEventCreate(&e0));
     CHECK_CUDA(cudaEventCreate(&e1));
     CHECK_CUDA(cudaEventRecord(e0));
-    for (int i = 0; i < runs; i++) CHECK_SL8(h, launch());
+    for (int i = 0; i < runs; i++) if (launch()) return 1;
     CHECK_CUDA(cudaEventRecord(e1));
     CHECK_CUDA(cudaEventSynchronize(e1));
-    float total_ms = 0;
-    CHECK_CUDA(cudaEventElapsedTime(&total_ms, e0, e1));
-    const double ms = total_ms / runs;
+    float total = 0;
+    CHECK_CUDA(cudaEventElapsedTime(&total, e0, e1));
+    st->total_ms = total / runs;
+    std::vector<cudaEvent_t> ev(2 * static_cast<size_t>(runs));
+    for (auto& e : ev) CHECK_CUDA(cudaEventCreate(&e));
+    for (int i = 0; i < runs; i++) {
+        CHECK_CUDA(cudaEventRecord(ev[2 * i]));
+        if (launch()) return 1;
+        CHECK_CUDA(cudaEventRecord(ev[2 * i + 1]));
+    }
+    CHECK_CUDA(cudaDeviceSynchronize());
+    std::vector<float> t(runs);
+    double sum = 0;
+    for (int i = 0; i < runs; i++) {
+        CHECK_CUDA(cudaEventElapsedTime(&t[i], ev[2 * i], ev[2 * i + 1]));
+        sum += t[i];
+    }
+    std::sort(t.begin(), t.end());
+    st->min_ms = t[0];
+    st->median_ms = t[runs / 2];
+    st->mean_ms = sum / runs;
+    for (auto& e : ev) cudaEventDestroy(e);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    return 0;
+}
+
+template <typename F>
+int sustain(F&& launch, double seconds, double est_ms, double* ms_out, long long* n_out) {
+    long long n = static_cast<long long>(seconds * 1e3 / est_ms);
+    if (n < 20) n = 20;
+    cudaEvent_t e0, e1;
+    CHECK_CUDA(cudaEventCreate(&e0));
+    CHECK_CUDA(cudaEventCreate(&e1));
+    CHECK_CUDA(cudaEventRecord(e0));
+    for (long long i = 0; i < n; i++) if (launch()) return 1;
+    CHECK_CUDA(cudaEventRecord(e1));
+    CHECK_CUDA(cudaEventSynchronize(e1));
+    float total = 0;
+    CHECK_CUDA(cudaEventElapsedTime(&total, e0, e1));
+    *ms_out = total / n;
+    *n_out = n;
+    return 0;
+}
+
+struct Problem {
+    int op;                       // SL8_OP_*, or 3 = chain
+    long long M;
+    int N, K, period;
+    long long lda;                // row pitch of A and B (bytes)
+    uint8_t *A = nullptr, *B = nullptr, *B2 = nullptr, *H = nullptr;
+    float *bias = nullptr, *bias2 = nullptr, *pos = nullptr, *scales = nullptr;    // scales: a, b, hidden, b2 (all 1 for the constants)
+    __nv_bfloat16 *C = nullptr, *table = nullptr, *res = nullptr;
+    int table_rows = 0;
+    bool random = false;
+};
+constexpr int OP_CHAIN = 3;
+constexpr int D_MODEL = 1152, D_FF = 4304;
+
+int fill_codes(uint8_t* p, long long rows, int cols, long long pitch, bool random, unsigned seed, int max_exp, int constant) {
+    if (random) {
+        const long long total = rows * pitch;
+        fill_random_codes<<<static_cast<unsigned>((total + 255) / 256), 256>>>(p, rows, cols, pitch, seed, max_exp);
+        CHECK_CUDA(cudaGetLastError());
+    } else {
+        CHECK_CUDA(cudaMemset(p, constant, static_cast<size_t>(rows) * pitch));
+    }
+    return 0;
+}
+
+int alloc_problem(sl8_handle_t h, Problem& q) {
+    const long long M = q.M;
+    const int N = q.N, K = q.K;
+    CHECK_CUDA(cudaMalloc(&q.A, static_cast<size_t>(M) * q.lda));
+    CHECK_CUDA(cudaMalloc(&q.B, static_cast<size_t>(N) * q.lda));
+    CHECK_CUDA(cudaMalloc(&q.bias, static_cast<size_t>(N) * sizeof(float)));
+    CHECK_CUDA(cudaMalloc(&q.scales, 16));
+    const int out_n = q.op == OP_CHAIN ? D_MODEL : N;
+    CHECK_CUDA(cudaMalloc(&q.C, static_cast<size_t>(M) * out_n * sizeof(__nv_bfloat16)));
+    // random data: activations |x| < 4, weights |w| < 1/16 as codes, scales that bring the products to O(1)
+    if (fill_codes(q.A, M, K, q.lda, q.random, 1u, 8, 0x3C)) return 1;                     // constants: 1.5
+    if (q.random) {
+        if (fill_codes(q.B, N, K, q.lda, true, 2u, 5, 0)) return 1;
+    } else {
+        std::vector<uint8_t> hB(static_cast<size_t>(N) * q.lda, 0);
+        for (int n = 0; n < N; n++) memset(hB.data() + static_cast<size_t>(n) * q.lda, (n & 1) ? 0x38 : 0x3C, K);   // 1.0 / 1.5
+        CHECK_CUDA(cudaMemcpy(q.B, hB.data(), hB.size(), cudaMemcpyHostToDevice));
+    }
+    {
+        std::vector<float> hb(N);
+        for (int c = 0; c < N; c++) hb[c] = q.random ? 0.01f * static_cast<float>((c * 37) % 64 - 32) : static_cast<float>(c + 1);
+        CHECK_CUDA(cudaMemcpy(q.bias, hb.data(), N * sizeof(float), cudaMemcpyHostToDevice));
+        const float sc[4] = {1.0f, 1.0f, q.random ? 0.02f : 1.0f, 1.0f};
+        CHECK_CUDA(cudaMemcpy(q.scales, sc, 16, cudaMemcpyHostToDevice));
+    }
+    if (q.op == SL8_OP_PATCH_EMBED) {
+        std::vector<float> hp(static_cast<size_t>(q.period) * N);
+        for (int r = 0; r < q.period; r++)
+            for (int c = 0; c < N; c++)
+                hp[static_cast<size_t>(r) * N + c] = q.random ? 0.02f * static_cast<float>((r * 31 + c * 17) % 128 - 64) : 3.0f * static_cast<float>(r + 1);
+        CHECK_CUDA(cudaMalloc(&q.pos, hp.size() * sizeof(float)));
+        CHECK_CUDA(cudaMemcpy(q.pos, hp.data(), hp.size() * sizeof(float), cudaMemcpyHostToDevice));
+        q.table_rows = sl8_padded_table_rows(q.period);
+        CHECK_CUDA(cudaMalloc(&q.table, static_cast<size_t>(q.table_rows) * N * sizeof(__nv_bfloat16)));
+        CHECK_SL8(h, sl8_make_periodic_table(h, q.bias, q.pos, q.period, N, q.table, N, q.table_rows, 0));   // precompute_combined
+    }
+    if (q.op == SL8_OP_FC2_RESIDUAL || q.op == OP_CHAIN) {
+        const long long total = M * out_n;
+        CHECK_CUDA(cudaMalloc(&q.res, static_cast<size_t>(total) * sizeof(__nv_bfloat16)));
+        if (q.random) fill_random_bf16<<<static_cast<unsigned>((total + 255) / 256), 256>>>(q.res, total, 3u, 1.0f);
+        else fill_residual<<<static_cast<unsigned>((total + 255) / 256), 256>>>(q.res, out_n, total);
+        CHECK_CUDA(cudaGetLastError());
+    }
+    if (q.op == OP_CHAIN) {
+        const long long ldh = (D_FF + 127) / 128 * 128;
+        CHECK_CUDA(cudaMalloc(&q.H, static_cast<size_t>(M) * ldh));
+        CHECK_CUDA(cudaMalloc(&q.B2, static_cast<size_t>(D_MODEL) * ldh));
+        CHECK_CUDA(cudaMalloc(&q.bias2, D_MODEL * sizeof(float)));
+        if (fill_codes(q.B2, D_MODEL, D_FF, ldh, true, 4u, 5, 0)) return 1;
+        CHECK_CUDA(cudaMemset(q.bias2, 0, D_MODEL * sizeof(float)));
+    }
+    CHECK_CUDA(cudaDeviceSynchronize());
+    return 0;
+}
+
+void free_problem(Problem& q) {
+    cudaFree(q.A); cudaFree(q.B); cudaFree(q.bias); cudaFree(q.C); cudaFree(q.scales);
+    if (q.pos) cudaFree(q.pos);
+    if (q.table) cudaFree(q.table);
+    if (q.res) cudaFree(q.res);
+    if (q.H) cudaFree(q.H);
+    if (q.B2) cudaFree(q.B2);
+    if (q.bias2) cudaFree(q.bias2);
+}
+
+int launch_new(sl8_handle_t h, const Problem& q, cudaStream_t s) {
+    const float* sa = q.random ? q.scales : nullptr;   // the reference harness consumes raw codes: scale 1
+    const float* sb = q.random ? q.scales + 1 : nullptr;
+    if (q.op == SL8_OP_PATCH_EMBED)
+        return sl8_patch_embed_fp8(h, q.A, q.lda, q.B, q.lda, sa, sb, q.table, q.N, q.period, q.table_rows, 0, q.C, q.N, q.M, q.N, q.K, 0, s);
+    if (q.op == SL8_OP_FC1_GELU)
+        return sl8_fc1_gelu_fp8(h, q.A, q.lda, q.B, q.lda, sa, sb, q.bias, q.C, q.N, SL8_OUT_BF16, nullptr, q.M, q.N, q.K, SL8_FLAG_BIAS_F32, s);
+    if (q.op == SL8_OP_FC2_RESIDUAL)
+        return sl8_fc2_residual_fp8(h, q.A, q.lda, q.B, q.lda, sa, sb, q.bias, q.res, q.N, q.C, q.N, q.M, q.N, q.K, SL8_FLAG_BIAS_F32, s);
+    const long long ldh = (D_FF + 127) / 128 * 128;
+    return sl8_mlp_chain_fp8(h, q.A, q.lda, q.B, q.lda, q.scales, q.scales + 1, q.bias, q.H, ldh, q.scales + 2, q.B2, ldh, q.scales + 3,
+                             q.bias2, q.res, D_MODEL, q.C, D_MODEL, q.M, D_MODEL, D_FF, SL8_FLAG_BIAS_F32, s);
+}
+
+// ---------------------------------------------------------------------------------------- cuBLASLt arm
+struct LtArm {
+    cublasLtHandle_t lt = nullptr;
+    cublasLtMatmulDesc_t desc = nullptr;
+    cublasLtMatrixLayout_t lw = nullptr, lx = nullptr, lc = nullptr;
+    cublasLtMatmulHeuristicResult_t algos[128];
+    int n_algos = 0;
+    void* ws = nullptr;
+    size_t ws_bytes = 256ull << 20;
+    float alpha = 1.0f, beta = 0.0f;
+    const void* cptr = nullptr;
+};
+
+// D[M, N] (row-major) = X[M, K] . W[N, K]^T as cuBLASLt sees it: column-major D^T [N, M] = W (transposed) x X.
+// epilogue: 0 = none, 1 = GELU_BIAS, 2 = BIAS; c_operand != NULL -> beta = 1 with that matrix as C.
+int lt_setup(LtArm& a, const Problem& q, int kk, int epilogue, const __nv_bfloat16* bias_bf16, const __nv_bfloat16* c_operand) {
+    if (!a.lt) CHECK_LT(cublasLtCreate(&a.lt));
+    if (!a.ws) CHECK_CUDA(cudaMalloc(&a.ws, a.ws_bytes));
+    if (a.desc) { cublasLtMatmulDescDestroy(a.desc); a.desc = nullptr; }
+    CHECK_LT(cublasLtMatmulDescCreate(&a.desc, CUBLAS_COMPUTE_32F, CUDA_R_32F));
+    const cublasOperation_t opT = CUBLAS_OP_T, opN = CUBLAS_OP_N;
+    CHECK_LT(cublasLtMatmulDescSetAttribute(a.desc, CUBLASLT_MATMUL_DESC_TRANSA, &opT, sizeof opT));
+    CHECK_LT(cublasLtMatmulDescSetAttribute(a.desc, CUBLASLT_MATMUL_DESC_TRANSB, &opN, sizeof opN));
+    const float* sw = q.scales + 1;    // cuBLASLt's A is the weight matrix
+    const float* sx = q.scales;
+    CHECK_LT(cublasLtMatmulDescSetAttribute(a.desc, CUBLASLT_MATMUL_DESC_A_SCALE_POINTER, &sw, sizeof sw));
+    CHECK_LT(cublasLtMatmulDescSetAttribute(a.desc, CUBLASLT_MATMUL_DESC_B_SCALE_POINTER, &sx, sizeof sx));
+    if (epilogue) {
+        const cublasLtEpilogue_t epi = epilogue == 1 ? CUBLASLT_EPILOGUE_GELU_BIAS : CUBLASLT_EPILOGUE_BIAS;
+        CHECK_LT(cublasLtMatmulDescSetAttribute(a.desc, CUBLASLT_MATMUL_DESC_EPILOGUE, &epi, sizeof epi));
+        CHECK_LT(cublasLtMatmulDescSetAttribute(a.desc, CUBLASLT_MATMUL_DESC_BIAS_POINTER, &bias_bf16, sizeof bias_bf16));
+        const cudaDataType_t bt = CUDA_R_16BF;
+        CHECK_LT(cublasLtMatmulDescSetAttribute(a.desc, CUBLASLT_MATMUL_DESC_BIAS_DATA_TYPE, &bt, sizeof bt));
+    }
+    if (!a.lw) {
+        CHECK_LT(cublasLtMatrixLayoutCreate(&a.lw, CUDA_R_8F_E4M3, kk, q.N, q.lda));
+        CHECK_LT(cublasLtMatrixLayoutCreate(&a.lx, CUDA_R_8F_E4M3, kk, q.M, q.lda));
+        CHECK_LT(cublasLtMatrixLayoutCreate(&a.lc, CUDA_R_16BF, q.N, q.M, q.N));
+    }
+    a.beta = c_operand ? 1.0f : 0.0f;
+    a.cptr = c_operand ? static_cast<const void*>(c_operand) : static_cast<const void*>(q.C);
+    cublasLtMatmulPreference_t pref;
+    CHECK_LT(cublasLtMatmulPreferenceCreate(&pref));
+    CHECK_LT(cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &a.ws_bytes, sizeof a.ws_bytes));
+    a.n_algos = 0;
+    const cublasStatus_t st = cublasLtMatmulAlgoGetHeuristic(a.lt, a.desc, a.lw, a.lx, a.lc, a.lc, pref, 128, a.algos, &a.n_algos);
+    cublasLtMatmulPreferenceDestroy(pref);
+    if (st != CUBLAS_STATUS_SUCCESS) a.n_algos = 0;
+    return 0;
+}
+
+int lt_launch(LtArm& a, const Problem& q, int algo, cudaStream_t s) {
+    return cublasLtMatmul(a.lt, a.desc, &a.alpha, q.B, a.lw, q.A, a.lx, &a.beta, a.cptr, a.lc, q.C, a.lc, &a.algos[algo].algo, a.ws,
+                          a.ws_bytes, s) == CUBLAS_STATUS_SUCCESS ? 0 : 1;
+}
+
+// Times every returned heuristic (2 warm-up + `runs` launches) and keeps the fastest.
+int lt_best(LtArm& a, const Problem& q, int runs, double* best_ms, int* best_algo) {
+    *best_ms = -1;
+    *best_algo = -1;
+    cudaEvent_t e0, e1;
+    CHECK_CUDA(cudaEventCreate(&e0));
+    CHECK_CUDA(cudaEventCreate(&e1));
+    for (int al = 0; al < a.n_algos; al++) {
+        bool ok = true;
+        for (int i = 0; i < 2 && ok; i++) ok = lt_launch(a, q, al, 0) == 0;
+        if (!ok || cudaDeviceSynchronize() != cudaSuccess) { (void)cudaGetLastError(); continue; }
+        CHECK_CUDA(cudaEventRecord(e0));
+        for (int i = 0; i < runs && ok; i++) ok = lt_launch(a, q, al, 0) == 0;
+        CHECK_CUDA(cudaEventRecord(e1));
+        CHECK_CUDA(cudaEventSynchronize(e1));
+        if (!ok) continue;
+        float t = 0;
+        CHECK_CUDA(cudaEventElapsedTime(&t, e0, e1));
+        if (*best_algo < 0 || t / runs < *best_ms) { *best_ms = t / runs; *best_algo = al; }
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------- reference arm
+typedef void (*ref_shape_fn)(long long*, int*, int*, int*, int*);
+typedef int (*ref_launch_fn)(const void*, const void*, const void*, void*, const void*, void*);
+typedef int (*ref_table_fn)(const float*, const float*, void*, void*);
+
+std::string exe_dir() {      // the checker libraries are looked up relative to this binary: <repo>/siglip_b200/lib/siglip_bench
+    char buf[4096];
+    const ssize_t n = readlink("/proc/self/exe", buf, sizeof buf - 1);
+    if (n > 0) {
+        buf[n] = 0;
+        std::string p(buf);
+        const size_t k = p.rfind('/');
+        if (k != std::string::npos) return p.substr(0, k);
+    }
+    return ".";
+}
+
+}  // namespace
+
+static int run_gpu_share(int device, int op, long long M, int N, int K, int period, bool random, int runs, double* ms_out) {
+    CHECK_CUDA(cudaSetDevice(device));
+    sl8_handle_t h = nullptr;
+    if (sl8_create(&h, device) != SL8_OK) { fprintf(stderr, "sl8_create(%d): %s\n", device, sl8_last_error_string(nullptr)); return 1; }
+    Problem q;
+    q.op = op; q.M = M; q.N = N; q.K = K; q.period = period; q.random = random;
+    q.lda = (K + 127) / 128 * 128;
+    if (alloc_problem(h, q)) return 1;
+    Stats st;
+    if (time_launches([&]() { return launch_new(h, q, 0) != SL8_OK; }, runs, &st)) return 1;
     unsigned detail[4];
     CHECK_SL8(h, sl8_device_status(h, 0, detail));
-    const double tflops = 2.0 * M * N * K / ms / 1e9;
-    printf("Custom kernel: %.3f ms  %.2f TFLOPS\n", ms, tflops);
+    *ms_out = st.total_ms;
+    free_problem(q);
+    sl8_destroy(h);
+    return 0;
+}
 
-    // ---- validation on the host: 32 spots + checksum (patch_embed.cu:249-306)
-    std::vector<__nv_bfloat16> hC(static_cast<size_t>(M) * N);
-    CHECK_CUDA(cudaMemcpy(hC.data(), d_C, hC.size() * sizeof(__nv_bfloat16), cudaMemcpyDeviceToHost));
+int main(int argc, char** argv) {
+    setbuf(stdout, NULL);
+    const char* layer = "pe";
+    const char* impl = "new";
+    const char* config = "";
+    long long M = 928256;
+    int N = -1, K = -1, period = 196, runs = 10, gpus = 1;
+    bool random = false, chain = false;
+    double sustain_s = 0;
+    long long cpu_rows = 2916;
+    for (int i = 1; i < argc; i++) {
+        if (!strcmp(argv[i], "--layer") && i + 1 < argc) layer = argv[++i];
+        else if (!strcmp(argv[i], "--op") && i + 1 < argc) { const char* o = argv[++i]; if (!strcmp(o, "chain")) chain = true; else layer = o; }
+        else if (!strcmp(argv[i], "--impl") && i + 1 < argc) impl = argv[++i];
+        else if (!strcmp(argv[i], "--M") && i + 1 < argc) M = atoll(argv[++i]);
+        else if (!strcmp(argv[i], "--N") && i + 1 < argc) N = atoi(argv[++i]);
+        else if (!strcmp(argv[i], "--K") && i + 1 < argc) K = atoi(argv[++i]);
+        else if (!strcmp(argv[i], "--period") && i + 1 < argc) period = atoi(argv[++i]);
+        else if (!strcmp(argv[i], "--runs") && i + 1 < argc) runs = atoi(argv[++i]);
+        else if (!strcmp(argv[i], "--gpus") && i + 1 < argc) gpus = atoi(argv[++i]);
+        else if (!strcmp(argv[i], "--sustain") && i + 1 < argc) sustain_s = atof(argv[++i]);
+        else if (!strcmp(argv[i], "--cpu-rows") && i + 1 < argc) cpu_rows = atoll(argv[++i]);
+        else if (!strcmp(argv[i], "--data") && i + 1 < argc) random = !strcmp(argv[++i], "random");
+        else if (!strcmp(argv[i], "--config") && i + 1 < argc) {
+            const char* c = config = argv[++i];
+            if (!strcmp(c, "C1")) { layer = "pe"; M = 6272; N = 768; K = 768; period = 196; }
+            else if (!strcmp(c, "C2")) { layer = "fc1"; M = 46656; N = 4304; K = 1152; }
+            else if (!strcmp(c, "C3")) { layer = "fc2"; M = 46656; N = 1152; K = 4304; }
+            else if (!strcmp(c, "C4")) { layer = "pe"; M = 186624; N = 1152; K = 588; period = 729; }
+            else if (!strcmp(c, "C5")) { chain = true; M = 746496; }
+            else { fprintf(stderr, "unknown config %s (C1..C5)\n", c); return 2; }
+        }
+        else {
+            fprintf(stderr, "usage: %s [--config C1..C5] [--layer pe|fc1|fc2 | --op chain] [--impl new|cublaslt|ref|cpu] [--M rows] [--N n] [--K k] "
+                            "[--period p] [--runs r] [--data constant|random] [--gpus n] [--sustain seconds]\n", argv[0]);
+            return 2;
+        }
+    }
+    int op = !strcmp(layer, "pe") ? SL8_OP_PATCH_EMBED : !strcmp(layer, "fc1") ? SL8_OP_FC1_GELU : !strcmp(layer, "fc2") ? SL8_OP_FC2_RESIDUAL : -1;
+    if (chain) { op = OP_CHAIN; layer = "chain"; N = D_FF; K = D_MODEL; random = true; }
+    if (op < 0) { fprintf(stderr, "unknown layer %s\n", layer); return 2; }
+    if (N < 0) N = op == SL8_OP_FC1_GELU ? 3072 : 768;
+    if (K < 0) K = op == SL8_OP_FC2_RESIDUAL ? 3072 : 768;
+    if (runs < 1) runs = 1;
+    const double flops = (op == OP_CHAIN ? 4.0 : 2.0) * static_cast<double>(M) * N * K;
+
+    // ---- several GPUs: the rows divided by image, one thread and one handle per GPU, no data crosses GPUs
+    if (gpus > 1) {
+        if (strcmp(impl, "new")) { fprintf(stderr, "--gpus applies to --impl new\n"); return 2; }
+        const long long per_image = op == SL8_OP_PATCH_EMBED ? period : 729;
+        const long long images = M / per_image;
+        std::vector<double> ms(gpus, 0.0);
+        std::vector<int> rc(gpus, 0);
+        std::vector<std::thread> th;
+        for (int g = 0; g < gpus; g++) {
+            const long long first = images * g / gpus, last = images * (g + 1) / gpus;
+            th.emplace_back([&, g, first, last]() { rc[g] = run_gpu_share(g, op, (last - first) * per_image, N, K, period, random, runs, &ms[g]); });
+        }
+        for (auto& t : th) t.join();
+        double worst = 0;
+        for (int g = 0; g < gpus; g++) { if (rc[g]) return 1; worst = std::max(worst, ms[g]); }
+        printf("%s on %d GPUs (rows divided by image): slowest GPU %.3f ms  %.2f TFLOPS  %.0f images/s\n", layer, gpus, worst, flops / worst / 1e9,
+               images / worst * 1e3);
+        printf("{\"layer\": \"%s\", \"impl\": \"new\", \"gpus\": %d, \"M\": %lld, \"N\": %d, \"K\": %d, \"ms\": %.4f, \"tflops\": %.2f, \"images_per_s\": %.1f}\n",
+               layer, gpus, M, N, K, worst, flops / worst / 1e9, images / worst * 1e3);
+        return 0;
+    }
+
+    // ---- CPU arm: the restatement in oracle/libsl8_oracle.so on a bounded number of rows
+    if (!strcmp(impl, "cpu")) {
+        if (op == OP_CHAIN) { fprintf(stderr, "--impl cpu covers the three layers\n"); return 2; }
+        const std::string so = exe_dir() + "/../../oracle/libsl8_oracle.so";
+        void* lib = dlopen(so.c_str(), RTLD_NOW);
+        if (!lib) { fprintf(stderr, "%s: %s (run `make -C oracle`)\n", so.c_str(), dlerror()); return 1; }
+        typedef int (*gemm_fn)(const uint8_t*, int64_t, const uint8_t*, int64_t, int64_t, int, int, float*, int64_t);
+        typedef int (*threads_fn)(void);
+        gemm_fn gemm = reinterpret_cast<gemm_fn>(dlsym(lib, "sl8o_gemm_fp8_f32"));
+        threads_fn nthreads = reinterpret_cast<threads_fn>(dlsym(lib, "sl8o_num_threads"));
+        if (!gemm || !nthreads) { fprintf(stderr, "oracle library lacks sl8o_gemm_fp8_f32\n"); return 1; }
+        const long long rows = std::min(M, cpu_rows);
+        const long long lda = (K + 127) / 128 * 128;
+        std::vector<uint8_t> A(static_cast<size_t>(rows) * lda, 0x3C), B(static_cast<size_t>(N) * lda, 0x38);
+        std::vector<float> acc(static_cast<size_t>(rows) * N);
+        const auto t0 = std::chrono::steady_clock::now();
+        if (gemm(A.data(), lda, B.data(), lda, rows, N, K, acc.data(), N)) { fprintf(stderr, "oracle GEMM failed\n"); return 1; }
+        const double s = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+        const double tf = 2.0 * rows * N * K / s / 1e12;
+        printf("CPU FP32-accumulate GEMM over dequantised e4m3 (%d threads): %lld of %lld rows in %.3f s  %.4f TFLOPS\n", nthreads(), rows, M, s, tf);
+        printf("{\"layer\": \"%s\", \"impl\": \"cpu\", \"M\": %lld, \"N\": %d, \"K\": %d, \"rows_timed\": %lld, \"seconds\": %.4f, \"tflops\": %.4f, \"cores\": %d}\n",
+               layer, M, N, K, rows, s, tf, nthreads());
+        return 0;
+    }
+
+    sl8_handle_t h = NULL;
+    if (sl8_create(&h, 0) != SL8_OK) { fprintf(stderr, "sl8_create: %s\n", sl8_last_error_string(NULL)); return 1; }
+    Problem q;
+    q.op = op; q.M = M; q.N = N; q.K = K; q.period = period; q.random = random;
+    q.lda = (K + 127) / 128 * 128;      // rows start on 128-byte lines
+
+    // ---- reference arm: the reference's own kernels, at the shape they were compiled for
+    if (!strcmp(impl, "ref")) {
+        if (op == OP_CHAIN) { fprintf(stderr, "--impl ref covers the three layers\n"); return 2; }
+        const bool so400m = (N != (op == SL8_OP_FC1_GELU ? 3072 : 768));
+        const std::string so = exe_dir() + "/../../oracle/_ref/libsl8_ref_" + layer + (so400m ? "_so400m.so" : ".so");
+        void* lib = dlopen(so.c_str(), RTLD_NOW);
+        if (!lib) { fprintf(stderr, "%s: %s (run `make -C oracle ref ref_so400m` where the reference checkout is)\n", so.c_str(), dlerror()); return 1; }
+        ref_shape_fn shape = reinterpret_cast<ref_shape_fn>(dlsym(lib, "sl8_ref_shape"));
+        ref_launch_fn rlaunch = reinterpret_cast<ref_launch_fn>(dlsym(lib, "sl8_ref_launch"));
+        ref_table_fn rtable = reinterpret_cast<ref_table_fn>(dlsym(lib, "sl8_ref_make_table"));
+        long long Mp; int Np, Kp, seq, trows;
+        shape(&Mp, &Np, &Kp, &seq, &trows);
+        if (Np < N || Kp < K || Mp < M || (op == SL8_OP_PATCH_EMBED && seq != period)) {
+            fprintf(stderr, "%s is compiled for M=%lld N=%d K=%d period=%d: it cannot run M=%lld N=%d K=%d\n", so.c_str(), Mp, Np, Kp, seq, M, N, K);
+            return 1;
+        }
+        // zero-padded operands of the compiled shape (dense pitch Kp, as the reference's tensor maps assume)
+        uint8_t *A, *B; float *bias, *pos = nullptr; __nv_bfloat16 *C, *side = nullptr, *res = nullptr;
+        CHECK_CUDA(cudaMalloc(&A, static_cast<size_t>(Mp) * Kp)); CHECK_CUDA(cudaMemset(A, 0, static_cast<size_t>(Mp) * Kp));
+        CHECK_CUDA(cudaMalloc(&B, static_cast<size_t>(Np) * Kp)); CHECK_CUDA(cudaMemset(B, 0, static_cast<size_t>(Np) * Kp));
+        if (random) {
+            fill_random_codes<<<static_cast<unsigned>((M * Kp + 255) / 256), 256>>>(A, M, K, Kp, 1u, 8);
+            fill_random_codes<<<static_cast<unsigned>((static_cast<long long>(N) * Kp + 255) / 256), 256>>>(B, N, K, Kp, 2u, 5);
+        } else {
+            CHECK_CUDA(cudaMemset2D(A, Kp, 0x3C, K, M));
+            std::vector<uint8_t> hB(static_cast<size_t>(Np) * Kp, 0);
+            for (int n = 0; n < N; n++) memset(hB.data() + static_cast<size_t>(n) * Kp, (n & 1) ? 0x38 : 0x3C, K);
+            CHECK_CUDA(cudaMemcpy(B, hB.data(), hB.size(), cudaMemcpyHostToDevice));
+        }
+        CHECK_CUDA(cudaMalloc(&bias, Np * sizeof(float))); CHECK_CUDA(cudaMemset(bias, 0, Np * sizeof(float)));
+        CHECK_CUDA(cudaMalloc(&C, static_cast<size_t>(Mp) * Np * 2));
+        const void* side_ptr = bias;
+        if (op == SL8_OP_PATCH_EMBED) {
+            CHECK_CUDA(cudaMalloc(&pos, static_cast<size_t>(seq) * Np * sizeof(float))); CHECK_CUDA(cudaMemset(pos, 0, static_cast<size_t>(seq) * Np * sizeof(float)));
+            CHECK_CUDA(cudaMalloc(&side, static_cast<size_t>(trows) * Np * 2));
+            if (!rtable || rtable(bias, pos, side, nullptr)) { fprintf(stderr, "reference table kernel failed\n"); return 1; }
+            side_ptr = side;
+        }
+        if (op == SL8_OP_FC2_RESIDUAL) { CHECK_CUDA(cudaMalloc(&res, static_cast<size_t>(Mp) * Np * 2)); CHECK_CUDA(cudaMemset(res, 0, static_cast<size_t>(Mp) * Np * 2)); }
+        CHECK_CUDA(cudaDeviceSynchronize());
+        Stats st;
+        if (time_launches([&]() { return rlaunch(A, B, side_ptr, C, res, nullptr) != 0; }, runs, &st)) return 1;
+        CHECK_CUDA(cudaDeviceSynchronize());
+        printf("Reference kernel (%s, compiled for M=%lld N=%d K=%d): %.3f ms  %.2f TFLOPS on the useful M=%lld N=%d K=%d\n", so400m ? "zero-padded So400m build" : "own shape",
+               Mp, Np, Kp, st.total_ms, flops / st.total_ms / 1e9, M, N, K);
+        printf("{\"layer\": \"%s\", \"impl\": \"ref\", \"M\": %lld, \"N\": %d, \"K\": %d, \"ms\": %.4f, \"ms_min\": %.4f, \"ms_median\": %.4f, \"ms_mean\": %.4f, "
+               "\"tflops\": %.2f, \"runs\": %d, \"operands\": \"%s\"}\n", layer, M, N, K, st.total_ms, st.min_ms, st.median_ms, st.mean_ms, flops / st.total_ms / 1e9,
+               runs, random ? "random codes" : "reference constants");
+        return 0;
+    }
+
+    sl8_config cfg;
+    CHECK_SL8(h, sl8_query_config(h, op == OP_CHAIN ? SL8_OP_FC1_GELU : op, op == OP_CHAIN ? SL8_OUT_E4M3 : SL8_OUT_BF16, M, N, K, &cfg));
+    printf("%s GEMM -- %s, [%lld,%d] x [%d,%d]^T, tile %dx%dx%d, cta_group::%d, %d stages, %d epilogue warps, grid %d\n",
+           layer, sl8_version(), M, K, N, K, cfg.tile_m, cfg.tile_n, cfg.tile_k, cfg.cta_group, cfg.stages, cfg.epi_warps, cfg.grid);
+    if (alloc_problem(h, q)) return 1;
+    printf("  Alloc + init done\n");
+
+    // ---- cuBLASLt arm
+    if (!strcmp(impl, "cublaslt")) {
+        if (op == OP_CHAIN) { fprintf(stderr, "--impl cublaslt covers the three layers\n"); return 2; }
+        const int kk = (K + 15) / 16 * 16;                 // cuBLASLt FP8 wants K % 16 == 0; the pad bytes of the rows are zero
+        __nv_bfloat16* bias16 = nullptr;
+        CHECK_CUDA(cudaMalloc(&bias16, N * sizeof(__nv_bfloat16)));
+        f32_to_bf16<<<(N + 255) / 256, 256>>>(q.bias, bias16, N);
+        __nv_bfloat16* tiled = nullptr;
+        if (op == SL8_OP_PATCH_EMBED) {
+            const long long total = M * N;
+            CHECK_CUDA(cudaMalloc(&tiled, static_cast<size_t>(total) * 2));
+            tile_table<<<static_cast<unsigned>((total + 255) / 256), 256>>>(q.table, period, N, tiled, total);
+        }
+        CHECK_CUDA(cudaDeviceSynchronize());
+        // this library's output on the same operands: what the fused cuBLASLt result is compared with
+        std::vector<__nv_bfloat16> mine(static_cast<size_t>(std::min<long long>(M, 512)) * N), theirs(mine.size());
+        CHECK_SL8(h, launch_new(h, q, 0));
+        CHECK_CUDA(cudaMemcpy(mine.data(), q.C, mine.size() * 2, cudaMemcpyDeviceToHost));
+        LtArm arm;
+        double gemm_ms = -1, fused_ms = -1;
+        int gemm_algo = -1, fused_algo = -1, n_gemm = 0, n_fused = 0;
+        if (lt_setup(arm, q, kk, 0, nullptr, nullptr)) return 1;
+        n_gemm = arm.n_algos;
+        if (lt_best(arm, q, runs, &gemm_ms, &gemm_algo)) return 1;
+        const int epi = op == SL8_OP_FC1_GELU ? 1 : op == SL8_OP_FC2_RESIDUAL ? 2 : 0;
+        const __nv_bfloat16* cop = op == SL8_OP_FC2_RESIDUAL ? q.res : op == SL8_OP_PATCH_EMBED ? tiled : nullptr;
+        if (lt_setup(arm, q, kk, epi, bias16, cop)) return 1;
+        n_fused = arm.n_algos;
+        if (lt_best(arm, q, runs, &fused_ms, &fused_algo)) return 1;
+        double max_rel = -1;
+        if (fused_algo >= 0) {
+            if (lt_launch(arm, q, fused_algo, 0)) return 1;
+            CHECK_CUDA(cudaMemcpy(theirs.data(), q.C, theirs.size() * 2, cudaMemcpyDeviceToHost));
+            double num = 0, den = 0;
+            for (size_t i = 0; i < mine.size(); i++) {
+                const double a = __bfloat162float(mine[i]), b = __bfloat162float(theirs[i]);
+                num = std::max(num, std::fabs(a - b));
+                den = std::max(den, std::fabs(a));
+            }
+            max_rel = den > 0 ? num / den : 0;
+        }
+        const char* fused_name = op == SL8_OP_FC1_GELU ? "GELU_BIAS epilogue" : op == SL8_OP_FC2_RESIDUAL ? "BIAS epilogue, residual as C, beta = 1"
+                                                                                                          : "table tiled to M rows as C, beta = 1";
+        printf("cuBLASLt FP8 per-tensor scales: GEMM only %.3f ms (%.2f TFLOPS, best of %d heuristics); fused [%s] %.3f ms (%.2f TFLOPS, best of %d); "
+               "max |fused - this library| / max |this library| on the first rows %.4f\n", gemm_ms, gemm_ms > 0 ? flops / gemm_ms / 1e9 : 0.0, n_gemm,
+               fused_name, fused_ms, fused_ms > 0 ? flops / fused_ms / 1e9 : 0.0, n_fused, max_rel);
+        printf("{\"layer\": \"%s\", \"impl\": \"cublaslt\", \"M\": %lld, \"N\": %d, \"K\": %d, \"k_padded\": %d, \"gemm_ms\": %.4f, \"gemm_heuristics\": %d, \"fused_ms\": %.4f, "
+               "\"fused_heuristics\": %d, \"fused\": \"%s\", \"max_rel_diff_vs_new\": %.5f, \"runs\": %d, \"operands\": \"%s\"}\n", layer, M, N, K, kk, gemm_ms, n_gemm,
+               fused_ms, n_fused, fused_name, max_rel, runs, random ? "random codes" : "reference constants");
+        free_problem(q);
+        sl8_destroy(h);
+        return (gemm_algo >= 0) ? 0 : 1;
+    }
+    if (strcmp(impl, "new")) { fprintf(stderr, "unknown --impl %s (new, cublaslt, ref, cpu)\n", impl); return 2; }
+
+    auto launch = [&]() -> int { return launch_new(h, q, 0) != SL8_OK; };
+    Stats st;
+    if (time_launches(launch, runs, &st)) { fprintf(stderr, "launch failed: %s\n", sl8_last_error_string(h)); return 1; }
+    const double ms = st.total_ms;
+    unsigned detail[4];
+    CHECK_SL8(h, sl8_device_status(h, 0, detail));
+    const double tflops = flops / ms / 1e9;
+    printf("Custom kernel: %.3f ms  %.2f TFLOPS\n", ms, tflops);
+    printf("  per launch: min %.3f  median %.3f  mean %.3f ms (%d launches, an event pair each)\n", st.min_ms, st.median_ms, st.mean_ms, runs);
+    double sustained_ms = 0;
+    long long sustained_n = 0;
+    if (sustain_s > 0) {
+        if (sustain(launch, sustain_s, ms, &sustained_ms, &sustained_n)) return 1;
+        printf("  sustained: %lld launches back to back, %.3f ms each  %.2f TFLOPS\n", sustained_n, sustained_ms, flops / sustained_ms / 1e9);
+    }
+
+    // ---- validation on the host: 32 spots + checksum (patch_embed.cu:249-306); closed forms need the constant operands
+    const int out_n = op == OP_CHAIN ? D_MODEL : N;
+    std::vector<__nv_bfloat16> hC(static_cast<size_t>(M) * out_n);
+    CHECK_CUDA(cudaMemcpy(hC.data(), q.C, hC.size() * sizeof(__nv_bfloat16), cudaMemcpyDeviceToHost));
     double cksum = 0;
     {
-        const long long stride = M * N / 1024;
+        const long long stride = M * out_n / 1024;
         for (int i = 0; i < 1024; i++) cksum += std::fabs(static_cast<double>(__bfloat162float(hC[static_cast<size_t>(i) * stride])));
     }
     int errors = 0;
-    for (int spot = 0; spot < 32; spot++) {
-        const long long row = spot * M / 32;
-        const int col = (spot * 47) % N;
-        const float gemm = static_cast<float>(K) * 1.5f * ((col & 1) ? 1.0f : 1.5f);
-        const float bias = static_cast<float>(col + 1);
-        float expect;
-        if (op == SL8_OP_PATCH_EMBED) {
-            const float comb = bf16_round(bias + 3.0f * static_cast<float>(row % period + 1));
-            expect = bf16_round(bf16_round(gemm) + comb);                                   // patch_embed.cu:281-292
-        } else if (op == SL8_OP_FC1_GELU) {
-            expect = bf16_round(gelu_host(gemm + bias));                                    // fc1_gelu.cu:207-211
-        } else {
-            const float res = bf16_round(static_cast<float>(row % 128) * 0.25f + static_cast<float>(col) * 0.125f);
-            expect = bf16_round(gemm + bias + res);                                         // fc2.cu:239-245
+    if (!random) {
+        for (int spot = 0; spot < 32; spot++) {
+            const long long row = spot * M / 32;
+            const int col = (spot * 47) % N;
+            const float gemm = static_cast<float>(K) * 1.5f * ((col & 1) ? 1.0f : 1.5f);
+            const float bias = static_cast<float>(col + 1);
+            float expect;
+            if (op == SL8_OP_PATCH_EMBED) {
+                const float comb = bf16_round(bias + 3.0f * static_cast<float>(row % period + 1));
+                expect = bf16_round(bf16_round(gemm) + comb);                                   // patch_embed.cu:281-292
+            } else if (op == SL8_OP_FC1_GELU) {
+                expect = bf16_round(gelu_host(gemm + bias));                                    // fc1_gelu.cu:207-211
+            } else {
+                const float res = bf16_round(static_cast<float>(row % 128) * 0.25f + static_cast<float>(col) * 0.125f);
+                expect = bf16_round(gemm + bias + res);                                         // fc2.cu:239-245
+            }
+            const float got = __bfloat162float(hC[static_cast<size_t>(row) * N + col]);
+            if (got != expect) {
+                if (errors < 5) printf("  MISMATCH at (%lld,%d): expected %.1f got %.1f\n", row, col, expect, got);
+                errors++;
+            }
         }
-        const float got = __bfloat162float(hC[static_cast<size_t>(row) * N + col]);
-        if (got != expect) {
-            if (errors < 5) printf("  MISMATCH at (%lld,%d): expected %.1f got %.1f\n", row, col, expect, got);
-            errors++;
-        }
+        printf("Validation: %d/32 spot checks passed%s\n", 32 - errors, errors == 0 ? "" : " -- FAILED");
+    } else {
+        // random operands have no closed form: the run is valid if no device wait expired and the output is finite
+        for (size_t i = 0; i < hC.size(); i += 997) if (!std::isfinite(__bfloat162float(hC[i]))) errors++;
+        printf("Validation: random operands -- %s (parity with the CPU oracle is the test suite's job)\n", errors == 0 ? "outputs finite" : "non-finite outputs -- FAILED");
     }
     const int valid = errors == 0;
-    printf("Validation: %d/32 spot checks passed%s\n", 32 - errors, valid ? "" : " -- FAILED");
     printf("Checksum (1024 strided, absolute values): %f\n", cksum);
     // the reference's parsers accept [0-9.] only: a non-negative fixed-notation checksum and |c0|
     printf("@@RESULT ms=%.3f tflops=%.2f checksum=%f valid=%d c0=%.1f\n", ms, tflops, cksum, valid,
            std::fabs(__bfloat162float(hC[0])));
-    printf("{\"layer\": \"%s\", \"M\": %lld, \"N\": %d, \"K\": %d, \"ms\": %.4f, \"tflops\": %.2f, \"valid\": %d, \"variant\": %d, "
-           "\"runs\": %d, \"operands\": \"reference constants\"}\n", layer, M, N, K, ms, tflops, valid, cfg.variant_id, runs);
+    printf("{\"layer\": \"%s\", \"impl\": \"new\", \"config\": \"%s\", \"M\": %lld, \"N\": %d, \"K\": %d, \"ms\": %.4f, \"ms_min\": %.4f, \"ms_median\": %.4f, \"ms_mean\": %.4f, "
+           "\"tflops\": %.2f, \"valid\": %d, \"variant\": %d, \"runs\": %d, \"sustained_ms\": %.4f, \"sustained_launches\": %lld, \"images_per_s\": %.1f, \"operands\": \"%s\"}\n",
+           layer, config, M, N, K, ms, st.min_ms, st.median_ms, st.mean_ms, tflops, valid, cfg.variant_id, runs, sustained_ms, sustained_n,
+           (M / static_cast<double>(op == SL8_OP_PATCH_EMBED ? period : 729)) / ms * 1e3, random ? "random codes" : "reference constants");
 
-    cudaFree(d_A); cudaFree(d_B); cudaFree(d_bias); cudaFree(d_C);
-    if (d_pos) cudaFree(d_pos);
-    if (d_table) cudaFree(d_table);
-    if (d_res) cudaFree(d_res);
+    free_problem(q);
     sl8_destroy(h);
     return valid ? 0 : 1;
 }
