@@ -306,7 +306,7 @@ int run(sl8_handle_t h, const Problem& q, cudaStream_t stream) {
     p.table_rows = q.table_rows;
     p.D = q.D;
     p.ldd = q.ldd;
-    p.flags = q.flags | (h->trace_coarse ? sl8::FLAG_COARSE_TRACE : 0u);
+    p.flags = q.flags | (h->trace_coarse ? sl8::FLAG_COARSE_TRACE : 0u) | (h->single_acc ? sl8::FLAG_SINGLE_ACC : 0u);
     p.wait_budget_ms = h->wait_budget_ms;
     p.status = h->d_status;
     p.prof = h->d_prof;
@@ -386,6 +386,8 @@ SL8_API int sl8_create(sl8_handle_t* out, int device) {
     }
     const char* mc = getenv("SL8_MAX_CLUSTERS");
     if (mc && *mc) h->max_clusters_override = atoi(mc);
+    const char* sa = getenv("SL8_SINGLE_ACC");
+    h->single_acc = sa && *sa == '1';
     const char* fv = getenv("SL8_FORCE_VARIANT");
     if (fv && *fv) {
         const int id = atoi(fv);

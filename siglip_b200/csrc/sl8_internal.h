@@ -57,6 +57,7 @@ struct sl8_context {
     uint32_t* d_status = nullptr;       // 4 words
     long long* d_prof = nullptr;        // tracing buffer, PROF_SLOTS per CTA, or null
     int prof_blocks = 0;
+    bool single_acc = false;            // SL8_SINGLE_ACC=1: measurement aid, one accumulator (no MMA / epilogue overlap)
     bool trace_coarse = false;          // sl8_trace_enable(h, 2): per-role totals only, untimed code paths
     int last_grid = 0;
     sl8_encode_tiled_fn encode = nullptr;

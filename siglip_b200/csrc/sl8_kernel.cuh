@@ -62,6 +62,7 @@ enum : int { OUT_BF16 = 0, OUT_E4M3 = 1 };
 // roles then run their untimed code paths, so the totals are those of the kernel as it runs without tracing.
 enum : unsigned { FLAG_BIAS_F32 = 1u, FLAG_PE_F32_ADD = 2u, FLAG_NO_ACTIVATION = 4u, FLAG_GELU_HW_TANH = 8u,
                   FLAG_COARSE_TRACE = 0x40000000u,
+                  FLAG_SINGLE_ACC = 0x20000000u,   // measurement aid (set by the library from SL8_SINGLE_ACC): one accumulator, no MMA / epilogue overlap
                   DBG_SKIP_SIDE = 0x100u, DBG_SKIP_GELU = 0x200u, DBG_SKIP_BIAS = 0x400u, DBG_SKIP_STORE = 0x800u,
                   DBG_SKIP_LOAD = 0x1000u, DBG_SKIP_EPILOGUE = 0x2000u, DBG_SKIP_MMA = 0x4000u,
                   DBG_SKIP_A = 0x8000u, DBG_SKIP_B = 0x10000u, DBG_SKIP_TMEM_LD = 0x20000u, DBG_SKIP_MATH = 0x40000u,
@@ -482,7 +483,10 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const bool tail = (tn == p.tiles_n - 1) && (p.tail_cols != TN);
                 const int b_rows = tail ? p.tail_cols / CG : T::B_ROWS;
                 const int nb = tn * TN + static_cast<int>(cta_rank) * b_rows;
-                const uint32_t stage_tx = static_cast<uint32_t>(T::A_BYTES + T::KATOMS * b_rows * 128);
+                // (measurement builds: DBG_SKIP_A / DBG_SKIP_B leave one operand's copies out; the MMAs then read stale shared memory)
+                const uint32_t stage_tx = static_cast<uint32_t>((SL8_DBG(p.flags, DBG_SKIP_A) ? 0 : T::A_BYTES) +
+                                                                (SL8_DBG(p.flags, DBG_SKIP_B) ? 0 : T::KATOMS * b_rows * 128));
+                const bool skip_mine = is_a ? SL8_DBG(p.flags, DBG_SKIP_A) : SL8_DBG(p.flags, DBG_SKIP_B);
                 const CUtensorMap* const bmap = tail ? &map_bt : &map_b;
                 for (int kb = 0; kb < p.k_blocks; kb++) {
                     const long long t0 = prof ? clock64() : 0;
@@ -497,10 +501,12 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         const uint32_t bar = full_bar_leader + 8 * stage;
                         if (is_a) {
                             if (cta_rank == 0) mbar_arrive_expect_tx(full_bar0 + 8 * stage, 2 * stage_tx);
+                            if (!skip_mine) {
 #pragma unroll
-                            for (int a = 0; a < T::KATOMS; a++)
-                                tma_load_2d_pair(a_dst + a * T::A_ATOM_BYTES, &map_a, kb * T::TILE_K + 128 * a, m0, bar);
-                        } else {
+                                for (int a = 0; a < T::KATOMS; a++)
+                                    tma_load_2d_pair(a_dst + a * T::A_ATOM_BYTES, &map_a, kb * T::TILE_K + 128 * a, m0, bar);
+                            }
+                        } else if (!skip_mine) {
 #pragma unroll
                             for (int a = 0; a < T::KATOMS; a++)
                                 tma_load_2d_pair(b_dst + a * T::B_ATOM_BYTES, bmap, kb * T::TILE_K + 128 * a, nb, bar);
@@ -659,8 +665,8 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 if (!ok) break;
                 if constexpr (CG == 2) mma_commit_pair(tfull_bar0 + 8 * acc, 0x3);
                 else mma_commit(tfull_bar0 + 8 * acc);
-                acc ^= 1;
-                if (acc == 0) acc_phase ^= 1u;
+                if (p.flags & FLAG_SINGLE_ACC) acc_phase ^= 1u;
+                else { acc ^= 1; if (acc == 0) acc_phase ^= 1u; }
             }
             if (prof_any) {
                 long long* slot = p.prof + static_cast<size_t>(blockIdx.x) * PROF_SLOTS;
@@ -845,8 +851,8 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     else mbar_arrive(tempty_bar0 + 8 * acc);
                 }
             }
-            acc ^= 1;
-            if (acc == 0) acc_phase ^= 1u;
+            if (p.flags & FLAG_SINGLE_ACC) acc_phase ^= 1u;
+            else { acc ^= 1; if (acc == 0) acc_phase ^= 1u; }
 
             if constexpr (HAS_BIAS) {
                 if (has_next) {
