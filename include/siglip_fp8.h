@@ -306,8 +306,11 @@ int sl8_set_variant(sl8_handle_t h, int variant_id);
  * the first wait that expired. */
 int sl8_device_status(sl8_handle_t h, sl8_stream_t stream, unsigned detail[4]);
 
-/* Wait budget in milliseconds for later launches on this handle (default 2000). */
+/* Wait budget for later launches on this handle, in milliseconds or microseconds (default 2 s).  A wait that
+ * parks its thread is checked against the budget about every 0.3 ms, a spinning one every few microseconds; in a CTA
+ * pair the CTA whose wait ran out tells its partner, so both leave at once. */
 int sl8_set_wait_budget_ms(sl8_handle_t h, int ms);
+int sl8_set_wait_budget_us(sl8_handle_t h, int64_t us);
 
 /* ---- in-kernel tracing ------------------------------------------------------------------
  * Counterpart of the reference's -DTIMING build (clock64 stamps in the MMA thread and the

@@ -306,8 +306,9 @@ int run(sl8_handle_t h, const Problem& q, cudaStream_t stream) {
     p.table_rows = q.table_rows;
     p.D = q.D;
     p.ldd = q.ldd;
-    p.flags = q.flags | (h->trace_coarse ? sl8::FLAG_COARSE_TRACE : 0u) | (h->single_acc ? sl8::FLAG_SINGLE_ACC : 0u);
-    p.wait_budget_ms = h->wait_budget_ms;
+    p.flags = q.flags | (h->trace_coarse ? sl8::FLAG_COARSE_TRACE : 0u) | (h->single_acc ? sl8::FLAG_SINGLE_ACC : 0u) |
+              (h->test_drop_b ? sl8::FLAG_TEST_DROP_B : 0u);
+    p.wait_budget_us = h->wait_budget_us;
     p.status = h->d_status;
     p.prof = h->d_prof;
 
@@ -386,6 +387,8 @@ SL8_API int sl8_create(sl8_handle_t* out, int device) {
     }
     const char* mc = getenv("SL8_MAX_CLUSTERS");
     if (mc && *mc) h->max_clusters_override = atoi(mc);
+    const char* td = getenv("SL8_TEST_DROP_B");      // test aid: see FLAG_TEST_DROP_B
+    h->test_drop_b = td && *td == '1';
     const char* sa = getenv("SL8_SINGLE_ACC");
     h->single_acc = sa && *sa == '1';
     const char* fv = getenv("SL8_FORCE_VARIANT");
@@ -821,10 +824,15 @@ SL8_API int sl8_device_status(sl8_handle_t h, sl8_stream_t stream, unsigned deta
     return fail(h, SL8_ERR_DEVICE_TIMEOUT, buf);
 }
 
-SL8_API int sl8_set_wait_budget_ms(sl8_handle_t h, int ms) {
-    if (!h || ms < 1) return SL8_ERR_INVALID_VALUE;
-    h->wait_budget_ms = static_cast<unsigned>(ms);
+SL8_API int sl8_set_wait_budget_us(sl8_handle_t h, int64_t us) {
+    if (!h || us < 1 || us > 4000000000ll) return SL8_ERR_INVALID_VALUE;
+    h->wait_budget_us = static_cast<unsigned>(us);
     return SL8_OK;
+}
+
+SL8_API int sl8_set_wait_budget_ms(sl8_handle_t h, int ms) {
+    if (ms < 1) return SL8_ERR_INVALID_VALUE;
+    return sl8_set_wait_budget_us(h, static_cast<int64_t>(ms) * 1000);
 }
 
 // =========================================================================== tracing

@@ -57,13 +57,14 @@ struct sl8_context {
     uint32_t* d_status = nullptr;       // 4 words
     long long* d_prof = nullptr;        // tracing buffer, PROF_SLOTS per CTA, or null
     int prof_blocks = 0;
+    bool test_drop_b = false;           // SL8_TEST_DROP_B=1: test aid, one operand copy is never issued so that a bounded wait expires
     bool single_acc = false;            // SL8_SINGLE_ACC=1: measurement aid, one accumulator (no MMA / epilogue overlap)
     bool trace_coarse = false;          // sl8_trace_enable(h, 2): per-role totals only, untimed code paths
     int last_grid = 0;
     sl8_encode_tiled_fn encode = nullptr;
     int forced_variant = -1;
     int max_clusters_override = 0;      // SL8_MAX_CLUSTERS: measurement aid, caps the persistent grid
-    unsigned wait_budget_ms = 2000;
+    unsigned wait_budget_us = 2000000;
     bool smem_attr_set[SL8_NUM_VARIANTS][sl8::K_COUNT] = {};
     int max_clusters[SL8_NUM_VARIANTS][sl8::K_COUNT] = {};
     std::mutex mu;          // the handle's state during one launch (map cache, attributes, error text)

@@ -62,6 +62,8 @@ enum : int { OUT_BF16 = 0, OUT_E4M3 = 1 };
 // roles then run their untimed code paths, so the totals are those of the kernel as it runs without tracing.
 enum : unsigned { FLAG_BIAS_F32 = 1u, FLAG_PE_F32_ADD = 2u, FLAG_NO_ACTIVATION = 4u, FLAG_GELU_HW_TANH = 8u,
                   FLAG_COARSE_TRACE = 0x40000000u,
+                  FLAG_TEST_DROP_B = 0x10000000u,  // test aid (set by the library from SL8_TEST_DROP_B): the B copy of k-block 1 of each cluster's first tile is
+                                                   // never issued, so the MMA thread's bounded wait for that stage runs out
                   FLAG_SINGLE_ACC = 0x20000000u,   // measurement aid (set by the library from SL8_SINGLE_ACC): one accumulator, no MMA / epilogue overlap
                   DBG_SKIP_SIDE = 0x100u, DBG_SKIP_GELU = 0x200u, DBG_SKIP_BIAS = 0x400u, DBG_SKIP_STORE = 0x800u,
                   DBG_SKIP_LOAD = 0x1000u, DBG_SKIP_EPILOGUE = 0x2000u, DBG_SKIP_MMA = 0x4000u,
@@ -121,7 +123,7 @@ struct KernelParams {
     void* D;
     long long ldd;                   // elements of the output type
     unsigned flags;
-    unsigned wait_budget_ms;
+    unsigned wait_budget_us;         // budget of every device-side wait, microseconds
     uint32_t* status;                // 4 words: code, barrier/stage, tile, block
     long long* prof;                 // optional: PROF_SLOTS clock64 totals per CTA (null = tracing off)
 };
@@ -169,6 +171,7 @@ struct KernelTraits {
 
 struct WaitCtx {
     volatile uint32_t* abort_flag;  // shared memory, one per CTA
+    uint32_t peer_abort;            // shared::cluster address of the other CTA's flag in a CTA pair, else 0
     uint32_t* status;
     unsigned long long budget_ns;
     uint32_t tile;
@@ -192,6 +195,8 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, const Wa
                 t0 = now;
             } else if (now - t0 > w.budget_ns) {
                 *w.abort_flag = 1u;
+                // the other CTA of a pair would otherwise sit out its own full budget on barriers only this CTA feeds
+                if (w.peer_abort) asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(w.peer_abort), "r"(1u) : "memory");
                 if (atomicCAS(w.status, 0u, code) == 0u) {
                     w.status[1] = which;
                     w.status[2] = w.tile;
@@ -412,7 +417,8 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     WaitCtx wc;
     wc.abort_flag = abort_flag;
     wc.status = p.status;
-    wc.budget_ns = static_cast<unsigned long long>(p.wait_budget_ms) * 1000000ull;
+    wc.budget_ns = static_cast<unsigned long long>(p.wait_budget_us) * 1000ull;
+    wc.peer_abort = (CG == 2) ? map_to_cta(smem_u32(const_cast<uint32_t*>(abort_flag)), cta_rank ^ 1u) : 0u;
     wc.tile = 0;
 
     // ---------------------------------------------------------------- set-up
@@ -488,6 +494,7 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                                                 (SL8_DBG(p.flags, DBG_SKIP_B) ? 0 : T::KATOMS * b_rows * 128));
                 const bool skip_mine = is_a ? SL8_DBG(p.flags, DBG_SKIP_A) : SL8_DBG(p.flags, DBG_SKIP_B);
                 const CUtensorMap* const bmap = tail ? &map_bt : &map_b;
+                const int drop_kb = (!is_a && (p.flags & FLAG_TEST_DROP_B) && tile == cluster_id) ? 1 : -1;   // evaluated once per tile
                 for (int kb = 0; kb < p.k_blocks; kb++) {
                     const long long t0 = prof ? clock64() : 0;
                     ok = wait_bar<SL8_SPIN_CRITICAL>(empty_bar0 + 8 * stage, phase ^ 1u, wc, ST_PRODUCER_EMPTY_WAIT, stage);
@@ -506,7 +513,7 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                 for (int a = 0; a < T::KATOMS; a++)
                                     tma_load_2d_pair(a_dst + a * T::A_ATOM_BYTES, &map_a, kb * T::TILE_K + 128 * a, m0, bar);
                             }
-                        } else if (!skip_mine) {
+                        } else if (!skip_mine && kb != drop_kb) {
 #pragma unroll
                             for (int a = 0; a < T::KATOMS; a++)
                                 tma_load_2d_pair(b_dst + a * T::B_ATOM_BYTES, bmap, kb * T::TILE_K + 128 * a, nb, bar);
@@ -518,7 +525,7 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
                             for (int a = 0; a < T::KATOMS; a++)
                                 tma_load_2d(a_dst + a * T::A_ATOM_BYTES, &map_a, kb * T::TILE_K + 128 * a, m0, bar);
-                        } else {
+                        } else if (kb != drop_kb) {
 #pragma unroll
                             for (int a = 0; a < T::KATOMS; a++)
                                 tma_load_2d(b_dst + a * T::B_ATOM_BYTES, bmap, kb * T::TILE_K + 128 * a, nb, bar);

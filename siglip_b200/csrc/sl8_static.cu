@@ -194,7 +194,7 @@ SL8_API int sl8_fc1_gelu_fp8_static(const void* A, int64_t lda, const void* B, i
     p.D = D;
     p.ldd = ldd;
     p.flags = flags;
-    p.wait_budget_ms = 2000;
+    p.wait_budget_us = 2000000;
     p.status = reinterpret_cast<uint32_t*>(s->scratch);                               // device address, from set-up
     p.prof = host_trace ? reinterpret_cast<long long*>(s->scratch + kTraceOffset) : nullptr;
 

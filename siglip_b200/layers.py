@@ -353,10 +353,15 @@ class Engine:
     def set_wait_budget_ms(self, ms: int) -> None:
         self._check(self._lib.sl8_set_wait_budget_ms(self._h, int(ms)))
 
+    def set_wait_budget_us(self, us: int) -> None:
+        self._check(self._lib.sl8_set_wait_budget_us(self._h, int(us)))
+
     def device_status(self, stream=None) -> None:
         """Synchronises the stream and raises SL8Error(SL8_ERR_DEVICE_TIMEOUT) if a device wait expired."""
         detail = (C.c_uint * 4)()
-        self._check(self._lib.sl8_device_status(self._h, self._stream(stream), C.byref(detail)))
+        rc = self._lib.sl8_device_status(self._h, self._stream(stream), C.byref(detail))
+        self.last_status_detail = tuple(int(x) for x in detail)      # (code, barrier / stage index, tile, block)
+        self._check(rc)
 
 
     # ------------------------------------------------------------------ tracing

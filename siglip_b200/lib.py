@@ -77,6 +77,7 @@ SIGNATURES = {
     "sl8_set_variant": (_I, [_P, _I]),
     "sl8_device_status": (_I, [_P, _P, C.POINTER(C.c_uint * 4)]),
     "sl8_set_wait_budget_ms": (_I, [_P, _I]),
+    "sl8_set_wait_budget_us": (_I, [_P, _I64]),
     "sl8_trace_enable": (_I, [_P, _I]),
     "sl8_trace_read": (_I, [_P, C.POINTER(C.c_longlong), _I]),
     "sl8_fc1_gelu_fp8_static": (_I, [_P, _I64, _P, _I64, _P, _P, _P, _P, _I64, _I, _P, _I64, _I, _I, _U, _P, _P, _P]),
