@@ -129,3 +129,75 @@ def test_full_size_chain_fc1_e4m3_into_fc2(engine, oracle):
     del p1
     p3 = synth.make_fc2(c3["M"], c3["N"], c3["K"], seed=0, device=DEV, act=H, act_scale=h_scale)
     check_full_size(engine, oracle, p3, "C3 on FC1's codes", seed=13)
+
+
+def committed_dispatch_rows():
+    """(op, N, K) -> sorted [(m_min, variant)] of the committed, generated dispatch table."""
+    import re
+    from pathlib import Path
+    text = (Path(__file__).resolve().parent.parent / "siglip_b200" / "csrc" / "sl8_dispatch_table.h").read_text()
+    ops = {"SL8_OP_PATCH_EMBED": 0, "SL8_OP_FC1_GELU": 1, "SL8_OP_FC2_RESIDUAL": 2}
+    table = {}
+    for op, n, k, m, v in re.findall(r"\{(SL8_OP_\w+), (\d+), (\d+), (\d+)LL, (\d+)\}", text):
+        table.setdefault((ops[op], int(n), int(k)), []).append((int(m), int(v)))
+    return {key: sorted(rows) for key, rows in table.items()}
+
+
+def table_variant(table, op, M, N, K):
+    rows = [v for m, v in table[(op, N, K)] if m <= M]
+    return rows[-1]
+
+
+def test_c5_chain_at_its_real_size(engine, oracle):
+    """C5 whole: 1024 images, M = 746 496 rows, through sl8_mlp_chain_fp8.  The hidden codes (FC1 -> e4m3) and the
+    output (FC2 on those very codes + residual) are checked on sampled row runs at tile edges, image edges, both ends
+    and seeded random places; the launches must pick the variants the committed sweep names for this M."""
+    d_model, d_ff, M = 1152, 4304, 1024 * 729
+    table = committed_dispatch_rows()
+    assert engine.query_config(synth.OP_FC1_GELU, M, d_ff, d_model, 1)["variant_id"] == table_variant(table, 1, M, d_ff, d_model)
+    assert engine.query_config(synth.OP_FC2_RESIDUAL, M, d_model, d_ff)["variant_id"] == table_variant(table, 2, M, d_model, d_ff)
+    p1 = synth.make_fc1(M, d_ff, d_model, seed=0, device=DEV)
+    w2 = synth.make_fc2(729, d_model, d_ff, seed=0, device=DEV)
+    g = torch.Generator(device=DEV).manual_seed(77)
+    residual = torch.empty((M, d_model), dtype=torch.bfloat16, device=DEV)
+    for r0 in range(0, M, 1 << 17):                                   # fp32 staging of the residual in slabs
+        r1 = min(M, r0 + (1 << 17))
+        residual[r0:r1] = torch.randn((r1 - r0, d_model), generator=g, device=DEV).to(torch.bfloat16)
+    h_scale = 0.0125
+    H = torch.empty((M, synth.pitch128(d_ff)), dtype=torch.uint8, device=DEV)[:, :d_ff]
+    D = engine.mlp_chain(p1.A, p1.B, p1.bias, w2.B, w2.bias, residual, scale_a=dscalar(p1.scale_a), scale_w1=dscalar(p1.scale_b),
+                         scale_w2=dscalar(w2.scale_b), hidden_scale=dscalar(h_scale), hidden=H)
+    engine.device_status()
+    assert bool(torch.isfinite(D.view(-1)[::9973].float()).all())
+    runs = sample_runs(M, seed=21, random_runs=16)
+    B1, B2 = p1.B.cpu().numpy(), w2.B.cpu().numpy()
+    got_h = np.concatenate([H[s:s + RUN].cpu().numpy() for s in runs])
+    ref_h = np.concatenate([oracle.fc1_gelu(np.ascontiguousarray(p1.A[s:s + RUN].cpu().numpy()), B1, p1.scale_a, p1.scale_b,
+                                            bits(p1.bias), out_e4m3=True, out_scale=h_scale) for s in runs])
+    check_e4m3(got_h, ref_h, "C5: hidden codes")
+    got_d = np.concatenate([bits(D[s:s + RUN]) for s in runs])
+    ref_d = np.concatenate([oracle.fc2_residual(np.ascontiguousarray(H[s:s + RUN].cpu().numpy()), B2, h_scale, w2.scale_b,
+                                                bits(w2.bias), bits(residual[s:s + RUN])) for s in runs])
+    check_bf16(got_d, ref_d, "C5: FC2 + residual on the hidden codes")
+
+
+@pytest.mark.parametrize("layer", ["fc1", "fc2", "pe"])
+def test_m_ladder_points_pick_the_committed_variant_and_match_the_oracle(engine, oracle, layer):
+    """The M ladder of the sweep (729 * 2^j rows, the sizes the dispatch table has break points for): at every point
+    the library picks the variant the committed table names, and sampled row runs match the oracle."""
+    table = committed_dispatch_rows()
+    op, N, K = {"fc1": (1, 4304, 1152), "fc2": (2, 1152, 4304), "pe": (0, 1152, 588)}[layer]
+    make = {"fc1": lambda M: synth.make_fc1(M, N, K, seed=3, device=DEV),
+            "fc2": lambda M: synth.make_fc2(M, N, K, seed=3, device=DEV),
+            "pe": lambda M: synth.make_patch_embed(M, N, K, 729, seed=3, device=DEV, pixels=True)}[layer]
+    for j in (0, 2, 4, 7, 8, 9):                      # 729 ... 373 248 rows (46 656 and 186 624 have tests of their own)
+        M = 729 * 2 ** j
+        assert engine.query_config(op, M, N, K)["variant_id"] == table_variant(table, op, M, N, K), f"{layer} M={M}"
+        p = make(M)
+        D = launch(engine, p, table=engine.padded_table(p.table) if p.table is not None else None)
+        runs = sample_runs(M, seed=30 + j, random_runs=6) if M > 2 * 729 else [0, M - RUN]
+        got = np.concatenate([bits(D[s:s + RUN]) for s in runs])
+        ref = np.concatenate([oracle_rows(oracle, p, s) for s in runs])
+        check_bf16(got, ref, f"{layer} M={M}: {len(runs)} runs of {RUN} rows")
+        del p, D
+        torch.cuda.empty_cache()
