@@ -273,6 +273,40 @@ def sustained_leg(fn, flops: float, device_index: int, seconds: float, barrier) 
     return out
 
 
+def trace_leg(eng, fn, p, ms_untraced: float) -> dict:
+    """SM clock cycles the kernel takes, from its own clock64 totals (tracing in its totals-only mode): the SM clock
+    inside the kernel (cycles / event time), cycles per tile and per k-block, how often the MMA thread found the
+    next stage still filling, and what the MMA thread and the epilogue waited for each other."""
+    eng.trace_enable(True, coarse=True)
+    for i in range(5):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n = 20
+    e0.record()
+    for i in range(n):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / n
+    rec = eng.trace_read()
+    eng.device_status()
+    eng.trace_enable(False)
+    cfg = eng.query_config(p.op, p.M, p.N, p.K)
+    lead = rec[::cfg["cta_group"]]                  # the CTAs that issue MMAs
+    tiles = sum(r["tiles"] for r in lead) / len(lead)
+    cyc = [r["mma_total"] for r in lead]
+    kb = (p.K + cfg["tile_k"] - 1) // cfg["tile_k"]
+    mean = sum(cyc) / len(cyc)
+    return {"ms_per_launch_traced": ms, "ms_per_launch_untraced": ms_untraced, "cycles_max": max(cyc), "cycles_mean": mean,
+            "sm_ghz_in_kernel": max(cyc) / ms / 1e6, "tiles_per_cluster": tiles, "cycles_per_tile": mean / tiles,
+            "cycles_per_k_block": mean / tiles / kb, "k_blocks_per_tile": kb,
+            "k_blocks_whose_operands_were_late_pct": 100.0 * sum(r["mma_wait_operands"] for r in lead) / len(lead) / tiles / kb,
+            "mma_waits_for_accumulator_cycles_per_tile": sum(r["mma_wait_accumulator"] for r in lead) / len(lead) / tiles,
+            "epilogue_waits_for_accumulator_cycles_per_tile": sum(r["epi_wait_accumulator"] for r in rec) / len(rec) / tiles,
+            "note": "a tcgen05.mma of a CTA pair (M 256, N 256, K 32) takes 128 cycles: 512 per full k-block of four"}
+
+
 def host_link_bandwidth(dev, barrier, mib: int = 256) -> dict:
     """Pinned host <-> device copy rate of this rank with both directions (and every other rank) busy at once."""
     n = mib << 20
@@ -547,6 +581,8 @@ def main() -> None:
     ap.add_argument("--images", type=int, default=None, help="override the batch (profiling captures use a smaller case)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-operand legs (profiling captures)")
     ap.add_argument("--only-headline", action="store_true", help="headline launches only: what a profiler capture wants")
+    ap.add_argument("--trace", action="store_true",
+                    help="add `trace`: in-kernel clock-cycle totals of the headline kernel (sl8_trace_enable, totals only: the hot loops stay untimed)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.only_headline:
@@ -619,6 +655,9 @@ def main() -> None:
     flops = p.flops()
     value = world * flops / ms_max / 1e9                      # TFLOP/s, all ranks
 
+    trace = None
+    if args.trace and rank == 0:
+        trace = trace_leg(eng, fn, p, ms)
     launch_stats = time_per_launch(fn, max(20, min(args.steps, 100))) if not args.only_headline else None
     sustained = None
     if not args.no_sustained:
@@ -696,6 +735,8 @@ def main() -> None:
             "images_per_s": world * n_images / ms_max * 1e3,
             "kernel_config": eng.query_config(p.op, p.M, p.N, p.K),
         }
+        if trace:
+            line["trace"] = trace
         if launch_stats:
             line["launch_stats"] = launch_stats
         if sustained:
