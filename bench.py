@@ -109,9 +109,11 @@ class ClockSampler:
         self._thread.join()
         k = int(len(self.samples) * skip_fraction)
         s = sorted(self.samples[k:])
-        pw = sorted(self.power[k:])
+        # NVML's power figure is a running average that lags the load by about a second: the last quarter of the
+        # samples is the closest this leg gets to the settled value; the maximum is reported beside it
+        pw = sorted(self.power[(3 * len(self.power)) // 4:])
         out = {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.sm_max, "reasons": sorted(self.reasons),
-               "samples": len(s), "power_w": pw[len(pw) // 2] if pw else None}
+               "samples": len(s), "power_w": pw[len(pw) // 2] if pw else None, "power_w_max": max(self.power) if self.power else None}
         if len(s) < 10:
             out["note"] = "fewer than 10 NVML samples fit into the timed region: see `sustained` for clocks under load"
         return out
