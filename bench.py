@@ -44,6 +44,12 @@ METRICS = {"C1": "fp8_tflops_patch_embed", "C2": METRIC, "C3": "fp8_tflops_fc2_r
 UNIT = "TFLOP/s"
 
 
+# DRAM bytes per launch of each layer's kernel at the FULL size of its configuration (dram__bytes_read.sum +
+# dram__bytes_write.sum, one-pass ncu capture of launches 11 - 19 of this bench with the caches left as the previous
+# launch left them: profiles/dram_traffic_full_size.md), per GEMM row so that a changed batch scales it.
+NCU_DRAM_BYTES_PER_ROW = {"C2": (53.9e6 + 401.2e6) / 46656, "C3": (310.7e6 + 108.0e6) / 46656, "C4": (119.6e6 + 428.5e6) / 186624}
+
+
 # ----------------------------------------------------------------------------- peaks
 def measured_peaks() -> dict:
     """Roofline denominators: the measured copy bandwidth and bf16 GEMM rate of this pool's B200s when
@@ -430,7 +436,7 @@ def layer_table(eng, dev, launches: int, peaks: dict, names=("C1", "C3", "C4"), 
         row = dict(st)
         row.update({"tflops": p.flops() / ms / 1e9, "gbs": p.min_bytes() / ms / 1e6,
                     "images_per_s": synth.CONFIGS[name]["images"] / ms * 1e3,
-                    "roofline": roofline_of(p, ms, peaks),
+                    "roofline": roofline_of(p, ms, peaks, traffic=NCU_DRAM_BYTES_PER_ROW[name] * p.M if name in NCU_DRAM_BYTES_PER_ROW else None),
                     "kernel_config": eng.query_config(p.op, p.M, p.N, p.K),
                     "workload": workload_config(name)["workload"]})
         fn2 = fn
@@ -743,9 +749,11 @@ def main() -> None:
             line["launch_stats"] = launch_stats
         if sustained:
             line["sustained"] = sustained
-        line["roofline"] = roofline_of(p, ms, peaks, traffic=None)
-        line["roofline"]["traffic_note"] = ("not reported: a small-case ncu capture ends with part of the output still dirty in L2, "
-                                            "so its DRAM byte count undercounts a full launch; profiles/ holds the captures")
+        per_row = NCU_DRAM_BYTES_PER_ROW.get(args.config)
+        line["roofline"] = roofline_of(p, ms, peaks, traffic=None if per_row is None else per_row * p.M)
+        line["roofline"]["traffic_note"] = ("DRAM bytes per launch from a one-pass ncu capture of this bench at full size, caches left as the "
+                                            "previous launch left them (profiles/dram_traffic_full_size.md); algorithmic bytes: "
+                                            f"{p.min_bytes():.0f}")
         line["roofline"]["power_note"] = ("the board sits at its 1 kW power cap under these kernels (sw_power_cap): the SM clock, not "
                                           "the tensor pipe or HBM, sets the rate; see `sustained`")
         if not args.no_cpu_baseline and world == 1:      # a reported baseline of the one-GPU run only
