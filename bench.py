@@ -689,7 +689,8 @@ def main() -> None:
         # ---- end to end: pinned host operands through the *_host entry point
         A_h = torch.zeros((p.M, p.A.stride(0)), dtype=torch.uint8).pin_memory()[:, :p.K]
         A_h.copy_(p.A)
-        B_h = p.B.cpu().pin_memory()
+        B_h = torch.zeros((p.N, p.B.stride(0)), dtype=torch.uint8).pin_memory()[:, :p.K]      # keeps the 16-byte row pitch of K = 588
+        B_h.copy_(p.B)
         D_h = torch.empty((p.M, p.N), dtype=torch.bfloat16).pin_memory()
         side_h = None
         if p.op == synth.OP_FC1_GELU:
