@@ -873,7 +873,9 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 }
             }
         }
-        if (lane == 0) tma_store_wait_all<0>();
+        // The staging buffers must have been read before this CTA's shared memory is given back; the writes themselves
+        // are complete for whoever is ordered after the kernel, as every write of a kernel is.
+        if (lane == 0) tma_store_wait_read<0>();
         __syncwarp();
         if (prof_total && lane == 0) {
             long long* slot = p.prof + static_cast<size_t>(blockIdx.x) * PROF_SLOTS;
