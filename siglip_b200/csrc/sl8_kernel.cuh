@@ -364,6 +364,54 @@ __device__ __forceinline__ void epilogue_16(const float (&v)[32], const EpiCtx& 
     if constexpr (OUT == OUT_BF16) sts128(a1, w[4], w[5], w[6], w[7]);
 }
 
+// FC1 on a whole 32-column chunk at once: sixteen independent element pairs go through the GELU's special-function
+// chain (ex2, rcp) together, which keeps that pipe fed with only two epilogue warps per scheduler.  Used by the variants
+// with up to eight epilogue warps (with sixteen, four warps per scheduler hide the chain and registers are scarce).
+template <int OUT, bool BSM>
+__device__ __forceinline__ void epilogue_32_fc1(const float (&v)[32], const EpiCtx& e, const float* bias32, float breg,
+                                                uint32_t region, int piece0) {
+    const uint64_t scale2 = pack_f32x2(e.scale, e.scale);
+    uint64_t g[16];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const float4 b = bias_quad<BSM>(bias32, breg, 0, i);
+        g[2 * i + 0] = fma_f32x2(pack_f32x2(v[4 * i + 0], v[4 * i + 1]), scale2, pack_f32x2(b.x, b.y));
+        g[2 * i + 1] = fma_f32x2(pack_f32x2(v[4 * i + 2], v[4 * i + 3]), scale2, pack_f32x2(b.z, b.w));
+    }
+    if (e.flags & FLAG_GELU_HW_TANH) {                                           // warp-uniform branches
+#pragma unroll
+        for (int i = 0; i < 16; i++) g[i] = gelu_hw_tanh_x2(g[i]);
+    } else if (!(e.flags & FLAG_NO_ACTIVATION) && !SL8_DBG(e.flags, DBG_SKIP_GELU)) {
+#pragma unroll
+        for (int i = 0; i < 16; i++) g[i] = gelu_tanh_x2(g[i]);
+    }
+    if constexpr (OUT == OUT_BF16) {
+        uint32_t w[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            float lo, hi;
+            unpack_f32x2(g[i], lo, hi);
+            w[i] = pack_bf16x2(lo, hi);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; q++)
+            sts128(region + e.row_off + (((piece0 + q) ^ e.swz) << 4), w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+    } else {
+        const uint64_t inv2 = pack_f32x2(e.inv_out, e.inv_out);
+        uint32_t w[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            float a, b, c, d;
+            unpack_f32x2(mul_f32x2(g[2 * i + 0], inv2), a, b);
+            unpack_f32x2(mul_f32x2(g[2 * i + 1], inv2), c, d);
+            w[i] = static_cast<uint32_t>(pack_e4m3x2(a, b)) | (static_cast<uint32_t>(pack_e4m3x2(c, d)) << 16);
+        }
+#pragma unroll
+        for (int q = 0; q < 2; q++)
+            sts128(region + e.row_off + (((piece0 + q) ^ e.swz) << 4), w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+    }
+}
+
 // Bias values of columns col0 + lane + 32 i (i < NB) as fp32; zero past N or without a bias.
 template <int NB>
 __device__ __forceinline__ void load_bias(float (&b)[NB], const void* bias, unsigned flags, int col0, int lane, int N) {
@@ -822,8 +870,13 @@ sl8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                     if (i == r * T::CHUNKS_PER_REGION + ch) breg = bcur[i];
                             }
                             if (!SL8_DBG(p.flags, DBG_SKIP_MATH)) {
-                                epilogue_16<OP, OUT, 0, BSM>(v, e, bias32, breg, region, piece0);
-                                if (n0 + c + 16 < p.N) epilogue_16<OP, OUT, 1, BSM>(v, e, bias32 + 16, breg, region, piece0 + T::OUT_BYTES);
+                                if constexpr (OP == OP_FC1 && EPI_WARPS <= 8) {
+                                    // (columns past N are computed on whatever the accumulator holds and clipped by the TMA store)
+                                    epilogue_32_fc1<OUT, BSM>(v, e, bias32, breg, region, piece0);
+                                } else {
+                                    epilogue_16<OP, OUT, 0, BSM>(v, e, bias32, breg, region, piece0);
+                                    if (n0 + c + 16 < p.N) epilogue_16<OP, OUT, 1, BSM>(v, e, bias32 + 16, breg, region, piece0 + T::OUT_BYTES);
+                                }
                             }
                             if (prof) t_math += clock64() - t0;
                         }
