@@ -2,9 +2,10 @@
 inference plug-in, a serving loop with a frozen memory pool).  Its status block and trace records live in a
 __device__ array inside the library instead of cudaMalloc'ed memory, so it needs no handle.
 
-Called twice in a row through the C ABI (the array keeps the previous call's contents, so the second call is
-the one that proves the clearing), each result compared with the handle-based sl8_fc1_gelu_fp8 on the same
-operands: same kernel, same arithmetic, so the outputs must be bit-identical.  This file sorts last on
+Called twice in a row through the C ABI (the array is shared by every call and keeps what the previous one left:
+the second call, with tracing on, runs on an array the first one has used), each result compared with the
+handle-based sl8_fc1_gelu_fp8 on the same operands: same arithmetic, so the outputs must be bit-identical, and the
+status words copied back must be zero although the host buffer was poisoned beforehand.  This file sorts last on
 purpose: a run that stops at the first failure has then already run every other test.
 """
 import ctypes as C
