@@ -14,8 +14,9 @@ Rank 0 prints ONE JSON line:
   launch_stats          the same launches timed one by one (an event pair per launch): min / median / mean;
   sustained             at least a second of back-to-back launches with NVML clock and power samples taken inside
                         it: what the kernel does once the 1 kW power cap has pulled the SM clock down;
-  layers                C1, C3, C4 (the other configurations), an event pair per launch, each with its roofline
-                        and the cuBLASLt FP8 GEMM on the same operands;
+  layers                C1, C3, C4 (the other configurations): an event pair per launch, the launches back to back,
+                        and the same launches replayed from a CUDA graph (a Python loop enqueues a 10 us kernel more
+                        slowly than the GPU runs it); each with its roofline and the cuBLASLt FP8 GEMM on the same operands;
   chain                 C5: FC1 + GELU -> e4m3 -> FC2 + residual on this rank's share of 1024 images (strong
                         scaling: the images are divided over the ranks), device-timed and end to end from pinned host
                         memory (sl8_mlp_chain_fp8_host);
@@ -239,6 +240,36 @@ def time_steps(fn, steps: int, warmup: int, barrier) -> float:
     return e0.elapsed_time(e1) / steps
 
 
+def time_graph_replay(fn, launches: int, replays: int = 4):
+    """ms per launch when `launches` calls are captured once into a CUDA graph and the graph is replayed: what the
+    GPU needs per launch when the host's enqueue cost (which bounds a Python loop around a kernel of a few
+    microseconds) is out of the way.  None if the capture fails."""
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(launches):
+                    fn(i)
+        torch.cuda.synchronize()
+        graph.replay()                                  # warm
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(replays):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / (replays * launches)
+        del graph
+        return ms
+    except Exception as exc:                            # a bench leg that cannot run must not take the line with it
+        sys.stderr.write(f"bench: graph replay skipped ({type(exc).__name__}: {exc})\n")
+        torch.cuda.synchronize()
+        return None
+
+
 def time_per_launch(fn, launches: int, warmup: int = 3) -> dict:
     """An event pair around every launch (on the launching stream): min / median / mean in ms."""
     for i in range(warmup):
@@ -455,11 +486,14 @@ def layer_table(eng, dev, launches: int, peaks: dict, names=("C1", "C3", "C4"), 
         st = time_per_launch(fn, launches)
         eng.device_status()
         b2b = time_steps(fn, launches, 3, lambda: None)          # no events between the launches
-        # the derived figures use the median of the per-launch times, or the back-to-back time where that is shorter:
-        # around a kernel of a few microseconds the two event records cost as much as the kernel itself
-        ms = min(st["ms_median"], b2b)
+        replay = time_graph_replay(fn, launches)                 # the same launches replayed from a CUDA graph
+        eng.device_status()
+        # the derived figures use the shortest of the three: around a kernel of a few microseconds the two event
+        # records cost as much as the kernel itself, and a Python loop enqueues more slowly than the GPU finishes
+        ms = min(t for t in (st["ms_median"], b2b, replay) if t)
         row = dict(st)
         row["ms_back_to_back"] = b2b
+        row["ms_graph_replay"] = replay
         row["ms_used_for_rates"] = ms
         row.update({"tflops": p.flops() / ms / 1e9, "gbs": p.min_bytes() / ms / 1e6,
                     "images_per_s": synth.CONFIGS[name]["images"] / ms * 1e3,
