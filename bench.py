@@ -199,6 +199,9 @@ def workload_config(name: str, images=None) -> dict:
 
 
 # ----------------------------------------------------------------------------- GPU arm
+IDLE_BEFORE_BURST_S = 1.0     # host sleep before a layer's burst legs (see layer_table)
+
+
 def launch_fn(eng, p, dev):
     """Returns (callable(i) launching one step on operand set i, number of sets, list of outputs)."""
     from siglip_b200 import synth
@@ -483,6 +486,11 @@ def layer_table(eng, dev, launches: int, peaks: dict, names=("C1", "C3", "C4"), 
     for name in names:
         p = synth.make_config(name, seed=0, device=dev)
         fn, _, _ = launch_fn(eng, p, dev)
+        # Like the headline, which is the first thing a fresh process times, each layer's bursts start from a GPU that
+        # has idled: right after seconds of dense launches the power limiter is still engaged and the same 20 launches
+        # take up to 20 % longer (patch-embed C4: 166 us after an idle second, 200 us right behind 2 s of FC1).
+        torch.cuda.synchronize()
+        time.sleep(IDLE_BEFORE_BURST_S)
         st = time_per_launch(fn, launches)
         eng.device_status()
         b2b = time_steps(fn, launches, 3, lambda: None)          # no events between the launches
@@ -495,6 +503,7 @@ def layer_table(eng, dev, launches: int, peaks: dict, names=("C1", "C3", "C4"), 
         row["ms_back_to_back"] = b2b
         row["ms_graph_replay"] = replay
         row["ms_used_for_rates"] = ms
+        row["idle_before_s"] = IDLE_BEFORE_BURST_S
         row.update({"tflops": p.flops() / ms / 1e9, "gbs": p.min_bytes() / ms / 1e6,
                     "images_per_s": synth.CONFIGS[name]["images"] / ms * 1e3,
                     "roofline": roofline_of(p, ms, peaks, traffic=NCU_DRAM_BYTES_PER_ROW[name] * p.M if name in NCU_DRAM_BYTES_PER_ROW else None),
@@ -574,6 +583,8 @@ def chain_leg(eng, dev, rank: int, world: int, barrier, dist, total_images: int,
         eng.mlp_chain(p1.A, p1.B, p1.bias, w2.B, w2.bias, residual, scale_a=sa1, scale_w1=sb1, scale_w2=sb2,
                       hidden_scale=h_scale, hidden=H, out=D)
 
+    torch.cuda.synchronize()
+    time.sleep(IDLE_BEFORE_BURST_S)              # the same starting point as the headline and the layers: an idle GPU
     ms = time_steps(step, steps, warmup, barrier)
     eng.device_status()
     t = torch.tensor([ms], device=dev, dtype=torch.float64)
