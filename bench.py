@@ -744,6 +744,10 @@ def main() -> None:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         sustained["ms_per_step_max_over_ranks"] = float(t)
         sustained["tflops_all_ranks"] = world * flops / float(t) / 1e9
+        # like against like: a second of launches against the cuBLAS bf16 GEMM held for seconds under the same power cap
+        sustained["peak_sustained"] = 2.0 * peaks["bf16_tflops_sustained"]
+        sustained["frac_of_sustained_peak"] = sustained["tflops"] / sustained["peak_sustained"]
+        sustained["peak_source"] = f"2 x sustained bf16 GEMM rate of {peaks['source']} MEASURED_PEAKS"
         eng.device_status()
 
     e2e_value, e2e_ms_max, e2e_steps, same, side_bytes = None, None, 0, True, 0
