@@ -395,7 +395,11 @@ def cublaslt_baseline(p, dev, steps: int) -> dict:
         else:
             imgs = p.M // p.period
             full = lambda i=0: gemm().view(imgs, p.period, p.N).add_(p.table)
+        torch.cuda.synchronize()
+        time.sleep(IDLE_BEFORE_BURST_S)          # the baseline starts from an idle GPU like the legs it is compared with
         t_gemm = time_steps(gemm, steps, 3, lambda: None)
+        torch.cuda.synchronize()
+        time.sleep(IDLE_BEFORE_BURST_S)
         t_full = time_steps(full, steps, 3, lambda: None)
         return {"torch_scaled_mm_gemm_ms": t_gemm, "torch_scaled_mm_gemm_tflops": p.flops() / t_gemm / 1e9,
                 "torch_scaled_mm_plus_epilogue_kernels_ms": t_full}
