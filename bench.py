@@ -252,7 +252,8 @@ def time_graph_replay(fn, launches: int, replays: int = 4):
         side.wait_stream(torch.cuda.current_stream())
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.stream(side):
-            with torch.cuda.graph(graph, stream=side):
+            # (thread-local capture mode: the NCCL watchdog and the NVML sampler threads are none of its business)
+            with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
                 for i in range(launches):
                     fn(i)
         torch.cuda.synchronize()
